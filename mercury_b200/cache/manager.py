@@ -40,11 +40,17 @@ class Sequence:
 
 class CacheManager:
     def __init__(self, group_windows: Seq[int], num_pages: int | Seq[int], page_size: int,
-                 num_slots: int):
+                 num_slots: int, keep_first: Seq[int] | None = None):
+        """`keep_first[g]`: a windowed group keeps the pages of its first `keep_first[g]`
+        tokens for as long as the sequence lives (tokens that every later query still
+        sees), besides the pages inside the window."""
         if page_size <= 0 or page_size & (page_size - 1):
             raise ValueError("page_size must be a positive power of two")
         self.page_size = page_size
         self.windows = [int(w) for w in group_windows]
+        self.keeps = [int(k) for k in (keep_first or [0] * len(self.windows))]
+        if len(self.keeps) != len(self.windows):
+            raise ValueError("one keep_first per group")
         counts = [num_pages] * len(self.windows) if isinstance(num_pages, int) else list(num_pages)
         self.pools = [PagePool(n, page_size) for n in counts]
         self.num_slots = num_slots
@@ -91,6 +97,10 @@ class CacheManager:
             return 0
         return max(0, next_position - window + 1) // self.page_size
 
+    def _kept_pages(self, group: int) -> int:
+        """Leading pages of a windowed group that are never given back."""
+        return -(-self.keeps[group] // self.page_size) if self.windows[group] > 0 else 0
+
     def _pages_for(self, length: int) -> int:
         return -(-length // self.page_size)
 
@@ -109,7 +119,9 @@ class CacheManager:
                 if self.windows[group] <= 0:
                     continue
                 first = self._first_needed(group, n * self.page_size)
-                if any(pool.lookup(hashes[i]) is None for i in range(first, n)):
+                kept = min(self._kept_pages(group), first)
+                if any(pool.lookup(hashes[i]) is None
+                       for i in list(range(kept)) + list(range(first, n))):
                     ok = False
                     break
             if ok:
@@ -138,18 +150,21 @@ class CacheManager:
         plans = []
         for group, pool in enumerate(self.pools):
             first = self._first_needed(group, hit * self.page_size) if hit else 0
+            kept = min(self._kept_pages(group), first)
+            head = [pool.lookup(hashes[i]) for i in range(kept)]
             reused = [pool.lookup(hashes[i]) for i in range(first, hit)]
-            pinned = sum(1 for p in reused if pool.ref[p] == 0)
+            pinned = sum(1 for p in head + reused if pool.ref[p] == 0)
             need_new = total - hit
             if need_new > pool.num_available() - pinned:
                 self.stats["allocation_failures"] += 1
                 return False
-            plans.append((first, reused, need_new))
-        for group, (first, reused, need_new) in enumerate(plans):
+            plans.append((first, head, reused, need_new))
+        for group, (first, head, reused, need_new) in enumerate(plans):
             pool = self.pools[group]
-            for page in reused:
+            for page in head + reused:
                 pool.hold(page)
-            table = [-1] * first + reused + [pool.take() for _ in range(need_new)]
+            table = (head + [-1] * (first - len(head)) + reused
+                     + [pool.take() for _ in range(need_new)])
             seq.tables[group] = table
             seq.committed[group] = hit
         seq.num_computed = hit * self.page_size
@@ -189,7 +204,8 @@ class CacheManager:
                         pool.commit(table[index], hashes[index])
                 seq.committed[group] = max(seq.committed[group], min(full, len(hashes)))
             first = self._first_needed(group, new_length)
-            for index in range(min(first, len(table)) - 1, -1, -1):
+            kept = self._kept_pages(group)
+            for index in range(min(first, len(table)) - 1, kept - 1, -1):
                 if table[index] < 0:
                     break
                 pool.release(table[index])

@@ -369,6 +369,186 @@ class KinelixConfig(ModelConfig):
         return out
 
 
+# --------------------------------------------------------------------------- Sisavik
+
+_SISAVIK_LATENT_KEYS = ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "scale")
+_SISAVIK_LEFT_KEYS = ("heads", "kv_heads", "dim", "vdim", "scale")
+_SISAVIK_RIGHT_KEYS = ("heads", "dim")
+
+
+@dataclass(frozen=True)
+class SisavikConfig(ModelConfig):
+    """A Sisavik decoder: layers whose sublayers read the stream through a short causal
+    convolution (x + conv(x), `canon.taps` taps per channel) and whose outputs pass an RMS
+    norm (weight stored around zero, applied as 1 + w) before they join the stream. A
+    layer's mixer is attention over a cached low-rank latent with a rotated key part shared
+    by all heads and a sliding window (`latent_attention`; with `kv_from: j` it reads the
+    rows layer j caches), or two mixers side by side whose outputs are added under
+    `left_scale` and `right_scale` (`parallel`): grouped-query attention with sigmoid
+    weights, values that are the keys as projected, a window and kept first tokens, beside
+    a generalized delta rule with a decay per key channel. The feed-forward is gelu-gated
+    and dense, or absent. The rows of the delta rule's low-rank decay map (`mix.right.w1`) are
+    a size that only the tensor gives; `sisavik_sizes_from_tensors` writes it into the mixer as
+    `right.decay_rank` when a model folder is read, and a configuration made in code names it
+    there. config.json keys: `architecture`, `width`, `vocab`, `norm.eps`,
+    `canon.taps` and `layers`, a list of `{"type", "mixer": {...}, "mlp": {"kind": "dense",
+    "ff"} | null}`. Positions are bounded by `max_positions` alone (not a key of the design;
+    absent, `DEFAULT_POSITIONS`)."""
+
+    width: int
+    vocab: int
+    norm_eps: float
+    taps: int = 1
+    max_positions: int = 1 << 20
+    layers: tuple = ()
+
+    DEFAULT_POSITIONS = 1 << 20
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "SisavikConfig":
+        def need(table, key: str, where: str) -> Any:
+            if not isinstance(table, dict) or key not in table:
+                raise ConfigError(f"config.json has no {key!r} in {where}, which Sisavik needs")
+            return table[key]
+
+        def positive(table, key: str, where: str) -> int:
+            value = int(need(table, key, where))
+            if value <= 0:
+                raise ConfigError(f"{where}: {key}={value} must be positive")
+            return value
+
+        def rotation(table: dict, limit: int, where: str) -> None:
+            rot = table.get("rot")
+            if not rot:
+                return
+            dims = int(need(rot, "dims", f"{where}'s rot"))
+            if dims < 0 or dims % 2 or dims > limit:
+                raise ConfigError(f"{where}: rot.dims={dims} must be even and at most {limit}")
+            if dims and float(need(rot, "base", f"{where}'s rot")) <= 0:
+                raise ConfigError(f"{where}: rot.base must be positive")
+
+        def mask(table: dict, where: str) -> None:
+            m = table.get("mask")
+            if not m:
+                return
+            if int(need(m, "size", f"{where}'s mask")) <= 0:
+                raise ConfigError(f"{where}: mask.size must be positive")
+            if int(m.get("keep_first", 0)) < 0:
+                raise ConfigError(f"{where}: mask.keep_first must not be negative")
+
+        layers = []
+        listed = need(raw, "layers", "the model")
+        for index, layer in enumerate(listed):
+            where = f"layer {index}"
+            kind = need(layer, "type", where)
+            mixer = dict(need(layer, "mixer", where))
+            if kind == "latent_attention":
+                for key in _SISAVIK_LATENT_KEYS:
+                    if key == "scale":
+                        float(need(mixer, key, f"{where}'s mixer"))
+                    elif key == "rot_dim":
+                        if int(need(mixer, key, f"{where}'s mixer")) < 0:
+                            raise ConfigError(f"{where}: rot_dim must not be negative")
+                    else:
+                        positive(mixer, key, f"{where}'s mixer")
+                rotation(mixer, int(mixer["rot_dim"]), where)
+                if int(mixer["rot_dim"]) and int((mixer.get("rot") or {}).get("dims", 0)) != int(mixer["rot_dim"]):
+                    raise ConfigError(f"{where}: rot.dims must equal rot_dim, the rotated key part")
+                mask(mixer, where)
+                source = mixer.get("kv_from")
+                if source is not None:
+                    source = int(source)
+                    ok = (0 <= source < index and listed[source].get("type") == "latent_attention"
+                          and listed[source].get("mixer", {}).get("kv_from") is None)
+                    if not ok:
+                        raise ConfigError(f"{where}: kv_from={source} must name an earlier "
+                                          f"latent-attention layer with a latent of its own")
+                    theirs = listed[source]["mixer"]
+                    same = (int(theirs.get("kv_rank", 0)) == int(mixer["kv_rank"])
+                            and int(theirs.get("rot_dim", -1)) == int(mixer["rot_dim"])
+                            and (theirs.get("rot") or {}) == (mixer.get("rot") or {}))
+                    if not same:
+                        raise ConfigError(f"{where}: kv_rank, rot_dim and rot differ from layer "
+                                          f"{source}'s, whose rows it reads")
+            elif kind == "parallel":
+                left = dict(need(mixer, "left", f"{where}'s mixer"))
+                right = dict(need(mixer, "right", f"{where}'s mixer"))
+                for key in _SISAVIK_LEFT_KEYS:
+                    if key == "scale":
+                        float(need(left, key, f"{where}'s left mixer"))
+                    else:
+                        positive(left, key, f"{where}'s left mixer")
+                if int(left["heads"]) % int(left["kv_heads"]):
+                    raise ConfigError(f"{where}: {left['heads']} query heads do not divide into "
+                                      f"{left['kv_heads']} key/value heads")
+                if int(left["vdim"]) != int(left["dim"]):
+                    raise ConfigError(f"{where}: the values are the keys, so vdim={left['vdim']} "
+                                      f"must equal dim={left['dim']}")
+                rotation(left, int(left["dim"]), f"{where}'s left mixer")
+                mask(left, f"{where}'s left mixer")
+                for key in _SISAVIK_RIGHT_KEYS:
+                    positive(right, key, f"{where}'s right mixer")
+                if "decay_rank" in right:
+                    positive(right, "decay_rank", f"{where}'s right mixer")
+                float(need(mixer, "left_scale", f"{where}'s mixer"))
+                float(need(mixer, "right_scale", f"{where}'s mixer"))
+            else:
+                raise ConfigError(f"{where}: mixer type {kind!r} is not one of latent_attention, "
+                                  f"parallel")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                mlp = dict(mlp)
+                if need(mlp, "kind", f"{where}'s mlp") != "dense":
+                    raise ConfigError(f"{where}: feed-forward kind {mlp['kind']!r} is not built")
+                positive(mlp, "ff", f"{where}'s mlp")
+            import copy
+
+            layers.append({"type": kind, "mixer": copy.deepcopy(layer["mixer"]), "mlp": mlp})
+        if not layers:
+            raise ConfigError("config.json lists no layers")
+        taps = int((raw.get("canon") or {}).get("taps", 1))
+        if not 1 <= taps <= 16:
+            raise ConfigError(f"canon.taps={taps}: a convolution over 1 to 16 tokens is built")
+        return cls(
+            architecture=str(raw.get("architecture") or (raw.get("architectures") or ["Sisavik"])[0]),
+            width=positive(raw, "width", "the model"),
+            vocab=positive(raw, "vocab", "the model"),
+            norm_eps=float(need(need(raw, "norm", "the model"), "eps", "norm")),
+            taps=taps,
+            max_positions=int(raw.get("max_positions") or cls.DEFAULT_POSITIONS),
+            layers=tuple(layers),
+        )
+
+    def to_dict(self) -> dict:
+        import copy
+
+        out = {
+            "architecture": self.architecture,
+            "width": self.width,
+            "vocab": self.vocab,
+            "norm": {"eps": self.norm_eps},
+            "canon": {"taps": self.taps},
+            "layers": [copy.deepcopy(l) for l in self.layers],
+        }
+        if self.max_positions != self.DEFAULT_POSITIONS:
+            out["max_positions"] = self.max_positions
+        return out
+
+
+def sisavik_sizes_from_tensors(raw: dict, shapes: dict) -> dict:
+    """The raw config.json with `mixer.right.decay_rank` of every parallel layer set to the
+    rows of its `l<i>.mix.right.w1`, where the configuration does not name it."""
+    import copy
+
+    out = copy.deepcopy(raw)
+    for index, layer in enumerate(out.get("layers") or []):
+        right = (layer.get("mixer") or {}).get("right") if isinstance(layer, dict) else None
+        shape = shapes.get(f"l{index}.mix.right.w1")
+        if isinstance(right, dict) and "decay_rank" not in right and shape:
+            right["decay_rank"] = int(shape[0])
+    return out
+
+
 # --------------------------------------------------------------------------- the registry
 
 @dataclass(frozen=True)
@@ -379,14 +559,20 @@ class Architecture:
     name: str
     config_class: type
     describe: Callable[[ModelConfig], Any]
+    # optional: (raw config.json, {tensor name: shape}) -> raw config.json with the sizes
+    # filled in that only a checkpoint's tensors give
+    complete: Callable[[dict, dict], dict] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_class: type, describe: Callable) -> None:
-    """Add an architecture. `describe(config)` returns the `ModelSpec` to build."""
-    _ARCHITECTURES[name] = Architecture(name, config_class, describe)
+def register_architecture(name: str, config_class: type, describe: Callable,
+                          complete: Callable | None = None) -> None:
+    """Add an architecture. `describe(config)` returns the `ModelSpec` to build. `complete(raw,
+    shapes)` (optional) fills sizes into a raw config.json that only the shapes of the
+    checkpoint's tensors give; it is called when a model folder is read."""
+    _ARCHITECTURES[name] = Architecture(name, config_class, describe, complete)
 
 
 def known_architectures() -> list[str]:
@@ -419,6 +605,11 @@ def read_model_config(folder: str | Path) -> tuple[Architecture, ModelConfig]:
     if not path.is_file():
         raise ConfigError(f"{path} does not exist")
     raw = json.loads(path.read_text())
+    entry = architecture_named(architecture_name(raw))
+    if entry.complete is not None:
+        from ..weights.loader import tensor_shapes
+
+        raw = entry.complete(raw, tensor_shapes(folder))
     return config_from_dict(raw)
 
 

@@ -67,6 +67,14 @@ class StepContext:
         # what one layer leaves for a later layer of the same pass (the values of a step's
         # tokens, say), by a key the model's description chose; emptied before every pass
         self.carry: dict = {}
+        # which of a block's mixers side by side is running (their outputs must not share a
+        # buffer); 0 for a block's only mixer
+        self.side = 0
+
+    def sublayer_out(self, rows: int, cols: int) -> torch.Tensor:
+        """The float32 buffer a sublayer leaves its output in, one per side."""
+        name = "sublayer_out" if not self.side else f"sublayer_out_{self.side}"
+        return self.workspace.get(name, rows, cols, "float32")
 
     def buffer(self, name: str, rows: int, cols: int, dtype=None) -> torch.Tensor:
         return self.workspace.get(name, rows, cols, dtype)
@@ -123,7 +131,8 @@ class ModelRunner:
         self.page_size = page_size
         self.max_seqs = max_seqs
         self.max_step_tokens = max_step_tokens
-        self.cache = CacheManager(self.model.group_windows, num_pages, page_size, max_seqs)
+        self.cache = CacheManager(self.model.group_windows, num_pages, page_size, max_seqs,
+                                  keep_first=self.model.group_keeps)
         self.kv_layers: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
         for cache_id, layer in self.model.cache_layers.items():
             pages = self.cache.pools[layer.group].num_pages
@@ -257,6 +266,7 @@ class ModelRunner:
         self.ctx.batch = batch
         self.ctx.carry.clear()
         self.ctx.prenormed = None
+        self.ctx.side = 0
         pin = getattr(self.ops, "pin_stream", None)
         if pin is None:
             return self.model.forward(self.ctx, self.kv_layers, self.states)

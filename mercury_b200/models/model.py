@@ -34,8 +34,8 @@ class Model:
             for block in self.blocks for mixer in block.mixers())
         # a request may start behind another request's cached pages only if every mixer's
         # memory of the prefix lies in those pages
-        self.skips_cached_prefix = all(mixer.skips_cached_prefix()
-                                       for block in self.blocks for mixer in block.mixers())
+        self.skips_cached_prefix = not self.keeps_block_state and all(
+            mixer.skips_cached_prefix() for block in self.blocks for mixer in block.mixers())
 
     # ------------------------------------------------------------------ layout of caches
 
@@ -62,20 +62,36 @@ class Model:
             for _m, mixer, cache_id in mixers:
                 if mixer.cache_need() is not None and cache_id not in needs:
                     raise ValueError(f"cache layer {cache_id} is read but no call stores it")
+        # a group: the cache layers that keep the same keys (the same window and the same
+        # number of kept first tokens), and so share block tables
         self.group_windows: list[int] = []
+        self.group_keeps: list[int] = []
         self.cache_layers: dict[int, CacheLayer] = {}
+        groups: list[tuple[int, int]] = []
         for cache_id in sorted(needs):
             window = needs[cache_id].window
-            if window not in self.group_windows:
-                self.group_windows.append(window)
-            self.cache_layers[cache_id] = CacheLayer(needs[cache_id], self.group_windows.index(window))
-        # per-request state, keyed by (schedule index, mixer index within the block)
+            key = (window, needs[cache_id].keep_first if window > 0 else 0)
+            if key not in groups:
+                groups.append(key)
+                self.group_windows.append(key[0])
+                self.group_keeps.append(key[1])
+            self.cache_layers[cache_id] = CacheLayer(needs[cache_id], groups.index(key))
+        # per-request state, keyed by (schedule index, mixer index within the block); the
+        # block's other stateful parts (`state_parts()`) follow its mixers
         self.state_needs: dict[tuple[int, int], StateNeed] = {}
-        for index, _call, mixers in self._calls():
+        for index, call, mixers in self._calls():
             for m, mixer, _cache_id in mixers:
                 need = mixer.state_need()
                 if need is not None:
                     self.state_needs[(index, m)] = need
+            for extra, part in enumerate(self._state_parts(self.blocks[call.block])):
+                self.state_needs[(index, len(mixers) + extra)] = part.state_need()
+        # a block that keeps state outside its mixers has to see every token as well
+        self.keeps_block_state = any(self._state_parts(block) for block in self.blocks)
+
+    @staticmethod
+    def _state_parts(block) -> list:
+        return list(getattr(block, "state_parts", lambda: [])())
 
     # ------------------------------------------------------------------ weights
 
@@ -132,7 +148,8 @@ class Model:
                 k, v = kv_layers[cache_id]
                 group = self.cache_layers[cache_id].group
                 caches.append(LayerCache(k, v, ctx.page_size, batch.tables[group], call.writes_cache))
-            own = [states.get((index, m)) for m in range(count)]
+            own = [states.get((index, m))
+                   for m in range(count + len(self._state_parts(block)))]
             # the norm that opens the next call's block, which this block's last product
             # may compute ahead (the final norm picks rows, so it is left alone)
             following = None

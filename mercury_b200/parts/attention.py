@@ -241,65 +241,130 @@ class MixedHeadAttention(Mixer):
 
 
 class LatentAttention(Mixer):
-    """Attention over a cached low-rank latent, without positions, with a softmax sink.
+    """Attention over a cached low-rank latent.
 
-    Per token: q = Wq h (heads x dim); c = rmsnorm(Wdkv h) * w, `rank` numbers, the only
-    thing the cache keeps; per head k = Wuk c and v = Wuv c; weights = exp(s_j) / (sum_j'
-    exp(s_j') + exp(sink_h)) over the keys j <= p with s = q.k * scale; an output projection.
+    Per token: q = Wq h (heads x dim), or through a latent of its own when `q_rank` is set:
+    q = Wuq (rmsnorm(Wdq h) * w_q); c = rmsnorm(Wdkv h) * w, `rank` numbers, which is what the
+    cache keeps; per head k = Wuk c and v = Wuv c; weights = softmax(q.k * scale) over the keys
+    j <= p (inside `window`, if one is given), with exp(sink_h) joining the denominator when
+    the layer has a `sink`; an output projection.
 
     The keys and values are never built. Since q.(Wuk_h c) = (Wuk_h^T q).c, a head's query is
     taken into the latent space once per token and the head attends over the cached rows
-    themselves, which serve as keys and as values (one shared head of size `rank` for all
-    query heads); Wuv_h is applied to the head's weighted sum of rows afterwards.
+    themselves, which serve as keys and as values (one shared head for all query heads);
+    Wuv_h is applied to the head's weighted sum of rows afterwards.
+
+    With `rot_dim` > 0 the down-projection has rot_dim more rows, which are not normed: one
+    rotated key part that all heads share. A head's query is then [dim unrotated | rot_dim
+    rotated] numbers, its score (q_u . k_u + q_r . k_r) * scale, and the cached row is
+    [c | k_r after rotation]: the query that meets it is [Wuk_h^T q_u | q_r rotated], and Wuv_h
+    reads the first `rank` numbers of the weighted sum of rows only. `position_encoding`
+    gives the rotation of those rot_dim numbers (tables and pairing).
 
     `own_latent=False`: the layer has no Wdkv and reads the rows that another layer's call
     stored (its `LayerCall` names that call's cache layer with `writes_cache=False`).
+    `cache_window`: what the cache layer keeps, where layers that read it look further back
+    than this one (default: this layer's own window).
     """
 
     capturable = True
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, rank: int,
                  scale: float, eps: float, prefix: str, own_latent: bool = True,
-                 names: dict | None = None):
+                 names: dict | None = None, sink: bool = True, q_rank: int = 0, rot_dim: int = 0,
+                 window: int = 0, cache_window: int | None = None,
+                 position_encoding: PartSpec | None = None):
         self.hidden_size, self.num_heads = hidden_size, num_heads
         self.head_dim, self.value_dim, self.rank = head_dim, value_dim, rank
         self.scale, self.eps, self.prefix = float(scale), float(eps), prefix
         self.own_latent = bool(own_latent)
-        self.q_size = num_heads * head_dim
-        self.names = {"q": "q", "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv",
+        self.has_sink = bool(sink)
+        self.q_rank, self.rot_dim = int(q_rank), int(rot_dim)
+        self.window = int(window)
+        self.cache_window = self.window if cache_window is None else int(cache_window)
+        if self.window and (self.cache_window and self.cache_window < self.window):
+            raise ValueError(f"{prefix}: the cache keeps {self.cache_window} keys, fewer than the "
+                             f"window of {self.window}")
+        self.position = None
+        if self.rot_dim:
+            if position_encoding is None:
+                raise ValueError(f"{prefix}: a rotated key part needs its position encoding")
+            self.position = build_part("position_encoding", position_encoding)
+            if getattr(self.position, "rotary_dim", 0) != self.rot_dim:
+                raise ValueError(f"{prefix}: the encoding must rotate all {self.rot_dim} numbers of "
+                                 f"the rotated part")
+        self.q_head = head_dim + self.rot_dim          # a head's query as projected
+        self.row = rank + self.rot_dim                 # a cached row
+        self.q_size = num_heads * self.q_head
+        self.names = {"q": "q", "q_down": "dq", "q_down_norm": "dq.norm", "q_up": "uq",
+                      "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv",
                       "sink": "sink", "o": "o"}
         self.names.update(names or {})
 
+    @property
+    def plain(self) -> bool:
+        """Neither a query latent nor a rotated part: the form whose kernels came first."""
+        return not self.q_rank and not self.rot_dim
+
     def cache_need(self):
-        return CacheNeed(1, self.rank, 0, shared_values=True)
+        return CacheNeed(1, self.row, self.cache_window, shared_values=True)
 
     def tensor_specs(self):
         p, n, h = self.prefix, self.names, self.hidden_size
-        specs = [TensorSpec(p + n["q"], (self.q_size, h))]
+        if self.q_rank:
+            specs = [TensorSpec(p + n["q_down"], (self.q_rank, h)),
+                     TensorSpec(p + n["q_down_norm"], (self.q_rank,), init="ones_normal", std=0.05),
+                     TensorSpec(p + n["q_up"], (self.q_size, self.q_rank), std=0.05)]
+        else:
+            specs = [TensorSpec(p + n["q"], (self.q_size, h))]
         if self.own_latent:
-            specs += [TensorSpec(p + n["down"], (self.rank, h)),
+            specs += [TensorSpec(p + n["down"], (self.row, h)),
                       TensorSpec(p + n["down_norm"], (self.rank,), init="ones_normal", std=0.05)]
-        return specs + [TensorSpec(p + n["up_k"], (self.q_size, self.rank)),
-                        TensorSpec(p + n["up_v"], (self.num_heads * self.value_dim, self.rank)),
-                        TensorSpec(p + n["sink"], (self.num_heads,), std=1.0),
-                        TensorSpec(p + n["o"], (h, self.num_heads * self.value_dim))]
+        specs += [TensorSpec(p + n["up_k"], (self.num_heads * self.head_dim, self.rank),
+                             std=0.02 if self.plain else 0.1),
+                  TensorSpec(p + n["up_v"], (self.num_heads * self.value_dim, self.rank),
+                             std=0.02 if self.plain else 0.1)]
+        if self.has_sink:
+            specs.append(TensorSpec(p + n["sink"], (self.num_heads,), std=1.0))
+        specs.append(TensorSpec(p + n["o"], (h, self.num_heads * self.value_dim)))
+        return specs + (self.position.tensor_specs() if self.position is not None else [])
 
     def load(self, tensors, setup):
         p, n = self.prefix, self.names
-        mats = [setup.place(tensors[p + n["q"]])]
+        mats = [setup.place(tensors[p + n["q_down" if self.q_rank else "q"]])]
+        self.down_norm = self.q_norm = self.q_up = None
+        if self.q_rank:
+            self.q_norm = setup.place(tensors[p + n["q_down_norm"]])
+            self.q_up = setup.place(tensors[p + n["q_up"]])
         if self.own_latent:
             mats.append(setup.place(tensors[p + n["down"]]))
             self.down_norm = setup.place(tensors[p + n["down_norm"]])
         widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
         self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()   # rows [q; dkv]
-        up_k = setup.place(tensors[p + n["up_k"]])
+        up_k = setup.place(tensors[p + n["up_k"]]).view(self.num_heads, self.head_dim, self.rank)
+        up_v = (setup.place(tensors[p + n["up_v"]]).view(self.num_heads, self.value_dim, self.rank)
+                .transpose(1, 2))
         # both per head and input-major, [heads, in, out]: the key up-projection as stored is the
         # map that takes a query to the latent (its transpose); the value up-projection is turned
-        self.absorb = up_k.view(self.num_heads, self.head_dim, self.rank).contiguous()
-        self.up_v = (setup.place(tensors[p + n["up_v"]]).view(self.num_heads, self.value_dim, self.rank)
-                     .transpose(1, 2).contiguous())
-        self.sink = setup.place(tensors[p + n["sink"]]).float().contiguous()
+        if self.rot_dim:
+            # the rotated part of a query passes into the place behind the latent unchanged,
+            # and the value up-projection does not read the rotated part of a row
+            absorb = torch.zeros((self.num_heads, self.q_head, self.row), dtype=up_k.dtype,
+                                 device=up_k.device)
+            absorb[:, :self.head_dim, :self.rank] = up_k
+            index = torch.arange(self.rot_dim, device=up_k.device)
+            absorb[:, self.head_dim + index, self.rank + index] = 1.0
+            widened = torch.zeros((self.num_heads, self.row, self.value_dim), dtype=up_v.dtype,
+                                  device=up_v.device)
+            widened[:, :self.rank] = up_v
+            self.absorb, self.up_v = absorb.contiguous(), widened.contiguous()
+        else:
+            self.absorb, self.up_v = up_k.contiguous(), up_v.contiguous()
+        self.sink = (setup.place(tensors[p + n["sink"]]).float().contiguous()
+                     if self.has_sink else None)
         self.out_weight = setup.place(tensors[p + n["o"]])
+        if self.position is not None:
+            self.position.load(tensors, setup)
 
     def forward(self, x, ctx, cache, state):
         tokens, ops = x.shape[0], ctx.ops
@@ -307,19 +372,145 @@ class LatentAttention(Mixer):
             raise ValueError(f"{self.prefix}: a layer stores latent rows iff it makes its own")
         pre = ctx.buffer("latent_in", tokens, self.in_weight.shape[0], dtype="float32")
         ops.linear(x, self.in_weight, None, pre)
-        if self.own_latent:
-            ops.latent_norm_store(pre, self.q_size, self.rank, self.down_norm, self.eps, ctx.batch, cache)
-        q = ctx.buffer("latent_q", tokens, self.num_heads * self.rank)
-        ops.head_linear(pre, 0, self.absorb, q)
-        gathered = ctx.buffer("latent_sum", tokens, self.num_heads * self.rank)
-        ops.paged_attention(q, self.num_heads, 1, self.rank, ctx.batch, cache, self.scale, 0,
-                            gathered, sinks=self.sink)
+        if self.plain:
+            if self.own_latent:
+                ops.latent_norm_store(pre, self.q_size, self.rank, self.down_norm, self.eps,
+                                      ctx.batch, cache)
+            queries = pre
+        else:
+            tables = self.position.rotary_tables() if self.position is not None else None
+            pairing = getattr(self.position, "pairing", "halves")
+            narrow = ctx.buffer("latent_cq", tokens, self.q_rank) if self.q_rank else None
+            # the query latent's norm, the key latent's norm, the rotation of the shared key
+            # part and the store of [c | rotated part] into the pages
+            ops.latent_prepare(pre, self.q_rank, self.q_norm, narrow,
+                               self.q_rank if self.q_rank else self.q_size, self.rank,
+                               self.down_norm, self.rot_dim, tables, pairing, self.eps, ctx.batch,
+                               cache if self.own_latent else None)
+            if self.q_rank:
+                queries = ctx.buffer("latent_qfull", tokens, self.q_size)
+                ops.linear(narrow, self.q_up, None, queries)
+            else:
+                queries = pre
+        q = ctx.buffer("latent_q", tokens, self.num_heads * self.row)
+        ops.head_linear(queries, 0, self.absorb, q)
+        if self.rot_dim:
+            ops.rope_rows(q, self.num_heads, self.row, self.rank, self.rot_dim, tables, pairing,
+                          ctx.batch)
+        gathered = ctx.buffer("latent_sum", tokens, self.num_heads * self.row)
+        ops.paged_attention(q, self.num_heads, 1, self.row, ctx.batch, cache, self.scale,
+                            self.window, gathered, sinks=self.sink)
         attended = ctx.buffer("attended_v", tokens, self.num_heads * self.value_dim)
         ops.head_linear(gathered, 0, self.up_v, attended)
-        out = ctx.buffer("sublayer_out", tokens, self.hidden_size, dtype="float32")
+        out = ctx.sublayer_out(tokens, self.hidden_size)
+        ops.linear(attended, self.out_weight, None, out)
+        return out
+
+
+class SigmoidAttention(Mixer):
+    """Grouped-query attention whose weights are sigmoids and are not normalised over the keys.
+
+    Per token: q = Wq h + bq (heads x dim), k = Wk h + bk (kv_heads x dim); the values are the
+    keys as projected (`values_from_keys`; before norm and rotation) or a projection of their
+    own; with `qk_norm`, q and k of each head are divided by their root mean square and
+    multiplied by a weight of `dim` numbers shared by the heads (plain weight), before the
+    rotation; the position encoding on q and k. Key j is seen from position p iff j <= p and
+    (p - j < window or j < keep_first): a sliding window beside first tokens that stay
+    visible at their true positions (window 0: every key). The weight of a seen key is
+    sigmoid(q.k * scale + b_h), b_h one learned number per query head; out_h = sum_j weight_j
+    v_j; an output projection.
+    """
+
+    capturable = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 scale: float, eps: float, prefix: str, window: int = 0, keep_first: int = 0,
+                 qk_norm: bool = True, qk_bias: bool = True, values_from_keys: bool = True,
+                 value_dim: int | None = None, names: dict | None = None, bias_suffix: str = ".b",
+                 position_encoding: PartSpec | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads do not divide into {num_kv_heads} groups")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim = head_dim
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
+        self.values_from_keys = bool(values_from_keys)
+        if self.values_from_keys and self.value_dim != head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        self.scale, self.eps, self.prefix = float(scale), float(eps), prefix
+        self.window, self.keep_first = int(window), int(keep_first) if window else 0
+        self.qk_norm, self.qk_bias = bool(qk_norm), bool(qk_bias)
+        self.position = (build_part("position_encoding", position_encoding)
+                         if position_encoding is not None else None)
+        self.q_size = num_heads * head_dim
+        self.k_size = num_kv_heads * head_dim
+        self.v_size = 0 if self.values_from_keys else num_kv_heads * self.value_dim
+        self.names = {"q": "q", "k": "k", "v": "v", "q_norm": "q.norm", "k_norm": "k.norm",
+                      "head_bias": "pb", "o": "o"}
+        self.names.update(names or {})
+        self.bias_suffix = bias_suffix
+
+    def cache_need(self):
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim,
+                         keep_first=self.keep_first)
+
+    def _projections(self):
+        return ("q", "k") if self.values_from_keys else ("q", "k", "v")
+
+    def tensor_specs(self):
+        p, n, b, h = self.prefix, self.names, self.bias_suffix, self.hidden_size
+        rows = {"q": self.q_size, "k": self.k_size, "v": self.v_size}
+        specs = []
+        for key in self._projections():
+            specs.append(TensorSpec(p + n[key], (rows[key], h), std=0.05))
+            if self.qk_bias and key != "v":
+                specs.append(TensorSpec(p + n[key] + b, (rows[key],), std=0.1))
+        if self.qk_norm:
+            specs += [TensorSpec(p + n["q_norm"], (self.head_dim,), init="ones_normal", std=0.1),
+                      TensorSpec(p + n["k_norm"], (self.head_dim,), init="ones_normal", std=0.1)]
+        specs += [TensorSpec(p + n["head_bias"], (self.num_heads,), std=0.5, mean=-2.0),
+                  TensorSpec(p + n["o"], (h, self.num_heads * self.value_dim))]
+        return specs + (self.position.tensor_specs() if self.position is not None else [])
+
+    def load(self, tensors, setup):
+        p, n, b = self.prefix, self.names, self.bias_suffix
+        mats = [setup.place(tensors[p + n[key]]) for key in self._projections()]
+        widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()
+        self.in_bias = None
+        if self.qk_bias:
+            biases = [setup.place(tensors[p + n[key] + b]) for key in ("q", "k")]
+            if self.v_size:
+                biases.append(torch.zeros(self.v_size, dtype=biases[0].dtype, device=biases[0].device))
+            self.in_bias = torch.cat([t.to(widest) for t in biases]).contiguous()
+        # norms are float32 arithmetic: their weights are held so
+        self.q_norm = self.k_norm = None
+        if self.qk_norm:
+            self.q_norm = setup.place(tensors[p + n["q_norm"]]).float().contiguous()
+            self.k_norm = setup.place(tensors[p + n["k_norm"]]).float().contiguous()
+        self.head_bias = setup.place(tensors[p + n["head_bias"]]).float().contiguous()
+        self.out_weight = setup.place(tensors[p + n["o"]])
+        if self.position is not None:
+            self.position.load(tensors, setup)
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops = x.shape[0], ctx.ops
+        pre = ctx.buffer("attn_in", tokens, self.in_weight.shape[0], dtype="float32")
+        ops.linear(x, self.in_weight, self.in_bias, pre)
+        tables = self.position.rotary_tables() if self.position is not None else None
+        pairing = getattr(self.position, "pairing", "halves")
+        layout = (self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+        q = ctx.buffer("attn_q", tokens, self.q_size)
+        # per-head norms, rotation, and the store of keys and values into the pages
+        ops.qk_norm_rope_store(pre, layout, self.q_norm, self.k_norm, self.eps, tables, pairing,
+                               ctx.batch, cache, q, self.values_from_keys)
+        attended = ctx.buffer("attended_v", tokens, self.num_heads * self.value_dim)
+        ops.sigmoid_attention(q, layout, ctx.batch, cache, self.scale, self.window,
+                              self.keep_first, self.head_bias, attended)
+        out = ctx.sublayer_out(tokens, self.hidden_size)
         ops.linear(attended, self.out_weight, None, out)
         return out
 
 
 register_mixer("mixed_head_attention", MixedHeadAttention)
 register_mixer("latent_attention", LatentAttention)
+register_mixer("sigmoid_attention", SigmoidAttention)

@@ -63,6 +63,9 @@ Arrangement (`register_arrangement`): how mixers, feed-forward and norms sit in 
                                               new pending delta (None if it is already in the
                                               stream); an arrangement with `first_norm()`
                                               also takes `next_norm=`
+    state_parts() -> list[Part]               optional: parts of the block other than mixers that
+                                              keep per-request state (each has `state_need()`);
+                                              their states follow the mixers' in `states`
 """
 
 from __future__ import annotations
@@ -101,13 +104,16 @@ class CacheNeed:
     window keeps the last `window` (pages behind it are given back). `value_dim` is the
     size of a value head where it differs from the key head's (0: the same). With
     `shared_values` one row per token serves as key and as value (a cached latent): no value
-    pages exist and a mixer is handed the key pages in their place."""
+    pages exist and a mixer is handed the key pages in their place. `keep_first`: with a
+    window, the pages of the first `keep_first` tokens are kept as well (tokens that stay
+    visible however far the window has moved on)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
     shared_values: bool = False
+    keep_first: int = 0
 
     @property
     def value_head_dim(self) -> int:

@@ -8,6 +8,7 @@ delta that is still to be added to it, and returns the delta it leaves behind.
 from __future__ import annotations
 
 from .base import Part, PartSpec, TensorSpec, build_part, register_arrangement
+from .convolution import build_input
 from .norm import scaled_add
 
 
@@ -153,6 +154,79 @@ class LayerScaleBlock:
         return None
 
 
+class PostNormBlock:
+    """A norm on each sublayer's output only: h <- h + norm(mixers(in(h))), then, where the
+    block has a feed-forward, h <- h + norm'(ff(in'(h))). What a sublayer reads is made from
+    the stream by an input part (`parts/convolution.py`: the stream plus a short causal
+    convolution of it, or the stream itself); those parts may keep per-request state, which
+    the block declares through `state_parts()`. The block may hold several mixers side by
+    side; all read the same input and their outputs are added under `mixer_scales` before
+    the norm (at most two are built). The sums into the stream are made by the norm behind
+    the sublayer, so the block leaves no pending delta."""
+
+    def __init__(self, hidden_size: int, mixers: list, mixer_post_norm: PartSpec,
+                 mixer_scales: list | None = None, mixer_input: PartSpec | None = None,
+                 feed_forward: PartSpec | None = None,
+                 feed_forward_post_norm: PartSpec | None = None,
+                 feed_forward_input: PartSpec | None = None):
+        if not 1 <= len(mixers) <= 2:
+            raise ValueError(f"a block of {len(mixers)} mixers side by side is not built (1 or 2)")
+        self._mixers = [build_part("mixer", m) for m in mixers]
+        self.mixer_scales = [float(v) for v in (mixer_scales or [1.0] * len(mixers))]
+        if len(self.mixer_scales) != len(self._mixers):
+            raise ValueError("one scale per mixer")
+        self.mixer_post_norm = build_part("norm", mixer_post_norm)
+        self.mixer_input = build_input(mixer_input, hidden_size)
+        self.feed_forward = self.feed_forward_post_norm = self.feed_forward_input = None
+        if feed_forward is not None:
+            if feed_forward_post_norm is None:
+                raise ValueError("a feed-forward needs the norm behind it")
+            self.feed_forward = build_part("feed_forward", feed_forward)
+            self.feed_forward_post_norm = build_part("norm", feed_forward_post_norm)
+            self.feed_forward_input = build_input(feed_forward_input, hidden_size)
+
+    def mixers(self):
+        return list(self._mixers)
+
+    def _inputs(self):
+        return [p for p in (self.mixer_input, self.feed_forward_input) if p is not None]
+
+    def state_parts(self):
+        return [p for p in self._inputs() if p.state_need() is not None]
+
+    def parts(self):
+        out = [self.mixer_input, *self._mixers, self.mixer_post_norm]
+        if self.feed_forward is not None:
+            out += [self.feed_forward_input, self.feed_forward, self.feed_forward_post_norm]
+        return out
+
+    def forward(self, h, delta, ctx, caches, states, next_norm=None):
+        if delta is not None:
+            raise ValueError("a post-norm block takes the stream with nothing pending")
+        count = len(self._mixers)
+        own = dict(zip(map(id, self.state_parts()), states[count:]))
+        x = self.mixer_input.forward(h, ctx, own.get(id(self.mixer_input)))
+        outs = []
+        for index, mixer in enumerate(self._mixers):
+            # mixers side by side leave their outputs in buffers of their own
+            ctx.side = index
+            outs.append(mixer.forward(x, ctx, caches[index], states[index]))
+        ctx.side = 0
+        if count == 1 and self.mixer_scales[0] == 1.0:
+            self.mixer_post_norm.normed_add(h, outs[0], ctx)
+        else:
+            self.mixer_post_norm.normed_add(h, outs[0], ctx,
+                                            second=outs[1] if count == 2 else None,
+                                            scales=(self.mixer_scales[0],
+                                                    self.mixer_scales[1] if count == 2 else 0.0))
+        if self.feed_forward is None:
+            return None
+        x = self.feed_forward_input.forward(h, ctx, own.get(id(self.feed_forward_input)))
+        self.feed_forward_post_norm.normed_add(h, self.feed_forward.forward(x, ctx), ctx)
+        return None
+
+
 register_arrangement("pre_norm", PreNormBlock)
+register_arrangement("post_norm", PostNormBlock)
 register_arrangement("pre_norm_layer_scale", LayerScaleBlock)
 register_arrangement("sandwich_norm", SandwichBlock)

@@ -64,9 +64,11 @@ class RMSNorm(Norm):
                  gain: str = "vector"):
         """`gain` "vector": one learned number per feature; "scalar": the checkpoint holds a
         single number for all features (it is spread over a vector when loaded, so the
-        kernels are the same)."""
-        if gain not in ("vector", "scalar"):
-            raise ValueError(f"gain={gain!r} is neither 'vector' nor 'scalar'")
+        kernels are the same); "one_plus": the checkpoint holds w around zero and the norm
+        multiplies by 1 + w (the sum is made once, in float32, when the weight is loaded, and
+        kept in float32 in both engines: 1 + w rounded to 16 bits would lose most of w)."""
+        if gain not in ("vector", "scalar", "one_plus"):
+            raise ValueError(f"gain={gain!r} is none of 'vector', 'scalar', 'one_plus'")
         self.size = size
         self.eps = eps
         self.weight_name = weight_name
@@ -75,6 +77,8 @@ class RMSNorm(Norm):
         self.weight = None
 
     def tensor_specs(self):
+        if self.gain == "one_plus":
+            return [TensorSpec(self.weight_name, (self.size,), std=self.init_std)]
         shape = (self.size,) if self.gain == "vector" else ()
         return [TensorSpec(self.weight_name, shape, init="ones_normal", std=self.init_std)]
 
@@ -82,17 +86,25 @@ class RMSNorm(Norm):
         weight = setup.place(tensors[self.weight_name])
         if self.gain == "scalar":
             weight = weight.reshape(1).expand(self.size).contiguous()
+        elif self.gain == "one_plus":
+            weight = (1.0 + weight.float()).contiguous()
         self.weight = weight
 
-    def normed_add(self, h, delta, ctx, then_norm=None):
+    def normed_add(self, h, delta, ctx, then_norm=None, second=None, scales=None):
         """h <- h + norm(delta): this norm applied to a sublayer's OUTPUT before it joins the
         float32 stream. With `then_norm` (an RMSNorm over the same width) the same kernel
-        also leaves that norm's output of the new stream in `ctx.prenormed`."""
+        also leaves that norm's output of the new stream in `ctx.prenormed`. With `second`
+        (the output of a mixer that ran beside the first) and `scales` (a, b) the norm is
+        taken of a * delta + b * second."""
         follow = then_norm if (isinstance(then_norm, RMSNorm) and then_norm.size == self.size) else None
         out = ctx.buffer("normed", h.shape[0], self.size) if follow is not None else None
+        extra = {}
+        if second is not None or scales is not None:
+            a, b = scales if scales is not None else (1.0, 1.0)
+            extra = {"delta2": second, "scale": float(a), "scale2": float(b)}
         ctx.ops.rmsnorm_add(h, delta, self.weight, self.eps,
                             follow.weight if follow is not None else None,
-                            follow.eps if follow is not None else 0.0, out)
+                            follow.eps if follow is not None else 0.0, out, **extra)
         ctx.prenormed = (follow, Computed(out)) if follow is not None else None
 
     def add_norm(self, h, delta, ctx, rows=None, defer=False):
@@ -163,3 +175,4 @@ def scaled_add(h, delta, scale, ctx, then_norm=None):
 register_norm("rmsnorm", RMSNorm)
 register_norm("layernorm", LayerNorm)
 register_norm("rmsnorm_scalar", lambda **params: RMSNorm(gain="scalar", **params))
+register_norm("rmsnorm_one_plus", lambda **params: RMSNorm(gain="one_plus", **params))

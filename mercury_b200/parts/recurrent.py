@@ -28,6 +28,12 @@ Delta Rule"): q, k, v through causal convolutions and SiLU; q, k to unit length 
            silu(Wg h)).
 Both keep S and the last taps - 1 inputs of their convolutions in one state row per
 request: [S | inputs one token back | two tokens back | ...].
+`GeneralizedDeltaRule`: r, k, v = Wr h, Wk h, Wv h (heads x dim each); a decay per head and key
+           channel, w = exp(-decay_scale * sigmoid(W2 tanh(W1 h) + w0)) (a low-rank map of the
+           input); a removal rate per head and key channel, a = sigmoid(Wa h + ba); with the unit
+           key u = k / sqrt(sum k^2 + unit_eps) of each head, S_t = diag(w) S_(t-1) - (a * u)
+           (u^T S_(t-1)) + k v^T, both terms reading the matrix as the token found it; o = S_t^T
+           r; out = Wo (o / rms(o) per head * w_norm * sigmoid(Wg h)). Its state is S alone.
 """
 
 from __future__ import annotations
@@ -290,7 +296,87 @@ class GatedDeltaRule(Mixer):
         return out
 
 
+class GeneralizedDeltaRule(Mixer):
+    capturable = True
+
+    def __init__(self, hidden_size: int, heads: int, key_dim: int, decay_rank: int, eps: float,
+                 prefix: str, head_dim: int | None = None, decay_scale: float = 0.6065306597126334,
+                 unit_eps: float = 1e-6, names: dict | None = None, bias_suffix: str = ".b"):
+        """`decay_scale`: the decay is exp(-decay_scale * sigmoid(.)), so a channel keeps at
+        least exp(-decay_scale) of its row per token; `decay_rank`: rows of W1."""
+        self.hidden_size, self.heads, self.key_dim = hidden_size, heads, key_dim
+        self.head_dim = key_dim if head_dim is None else int(head_dim)
+        self.decay_rank = int(decay_rank)
+        self.eps, self.unit_eps, self.prefix = float(eps), float(unit_eps), prefix
+        self.decay_scale = float(decay_scale)
+        self.keys = heads * key_dim
+        self.inner = heads * self.head_dim
+        # what one product reads off the layer's input: [r | k | v | g | a | t]
+        self.offsets = {"r": 0, "k": self.keys, "v": 2 * self.keys, "g": 2 * self.keys + self.inner,
+                        "a": 2 * self.keys + 2 * self.inner,
+                        "t": 3 * self.keys + 2 * self.inner}
+        self.proj = self.offsets["t"] + self.decay_rank
+        self.cells = heads * key_dim * self.head_dim
+        self.names = {"r": "r", "k": "k", "v": "v", "g": "g", "a": "a", "w1": "w1", "w2": "w2",
+                      "w0": "w0", "norm": "norm", "o": "o"}
+        self.names.update(names or {})
+        self.bias_suffix = bias_suffix
+
+    def state_need(self):
+        return StateNeed((self.cells,), torch.float32)
+
+    def tensor_specs(self):
+        p, n, h = self.prefix, self.names, self.hidden_size
+        return [TensorSpec(p + n["r"], (self.keys, h), std=0.05),
+                TensorSpec(p + n["k"], (self.keys, h), std=0.05),
+                TensorSpec(p + n["v"], (self.inner, h), std=0.05),
+                TensorSpec(p + n["g"], (self.inner, h), std=0.05),
+                TensorSpec(p + n["a"], (self.keys, h), std=0.05),
+                TensorSpec(p + n["a"] + self.bias_suffix, (self.keys,), std=0.5),
+                TensorSpec(p + n["w1"], (self.decay_rank, h), std=0.05),
+                TensorSpec(p + n["w2"], (self.keys, self.decay_rank), std=0.3),
+                TensorSpec(p + n["w0"], (self.keys,), std=1.0),
+                TensorSpec(p + n["norm"], (self.inner,), init="ones_normal", std=0.05),
+                TensorSpec(p + n["o"], (h, self.inner))]
+
+    def load(self, tensors, setup):
+        p, n = self.prefix, self.names
+        mats = [setup.place(tensors[p + n[key]]) for key in ("r", "k", "v", "g", "a", "w1")]
+        bias = setup.place(tensors[p + n["a"] + self.bias_suffix])
+        widest = (torch.float32 if any(t.dtype == torch.float32 for t in mats + [bias])
+                  else mats[0].dtype)
+        self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()
+        in_bias = torch.zeros(self.proj, dtype=widest, device=bias.device)
+        in_bias[self.offsets["a"]:self.offsets["a"] + self.keys] = bias.to(widest)
+        self.in_bias = in_bias.contiguous()
+        self.decay_weight = setup.place(tensors[p + n["w2"]])
+        self.decay_bias = setup.place(tensors[p + n["w0"]]).to(self.decay_weight.dtype).contiguous()
+        self.norm_weight = _float(setup, tensors[p + n["norm"]])
+        self.out_weight = setup.place(tensors[p + n["o"]])
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops, at = x.shape[0], ctx.ops, self.offsets
+        pre = ctx.buffer("recurrent_in", tokens, self.proj, dtype="float32")
+        ops.linear(x, self.in_weight, self.in_bias, pre)
+        # (float32: what makes the decay is 32-bit arithmetic)
+        squashed = ctx.buffer("recurrent_decay_in", tokens, self.decay_rank, dtype="float32")
+        ops.tanh_slice(pre, at["t"], self.decay_rank, squashed)
+        decay = ctx.buffer("recurrent_decay", tokens, self.keys, dtype="float32")
+        ops.linear(squashed, self.decay_weight, self.decay_bias, decay)
+        o = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
+        ops.general_delta_scan(pre, (at["r"], at["k"], at["v"], at["a"]), decay, self.decay_scale,
+                               (self.heads, self.key_dim, self.head_dim), self.unit_eps, state,
+                               ctx.batch, o, precise=ctx.dtype == torch.float32)
+        mixed = ctx.buffer("recurrent_mixed", tokens, self.inner)
+        ops.gated_group_norm(o, pre, at["g"], self.norm_weight, self.heads, self.eps, False, mixed,
+                             gate="sigmoid")
+        out = ctx.sublayer_out(tokens, self.hidden_size)
+        ops.linear(mixed, self.out_weight, None, out)
+        return out
+
+
 register_mixer("mingru", MinGRU)
+register_mixer("generalized_delta_rule", GeneralizedDeltaRule)
 register_mixer("mamba2", Mamba2)
 register_mixer("gated_delta_rule", GatedDeltaRule)
 register_mixer("gated_linear_recurrence", GatedLinearRecurrence)

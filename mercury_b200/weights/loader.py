@@ -56,6 +56,21 @@ def weight_files(folder: Path) -> list[Path]:
     return shards
 
 
+def tensor_shapes(folder: str | Path) -> dict[str, tuple[int, ...]]:
+    """`{name: shape}` of every tensor of the checkpoint under `folder`, read from the files'
+    headers alone ({} when the folder has no weights)."""
+    try:
+        files = weight_files(Path(folder))
+    except FileNotFoundError:
+        return {}
+    shapes: dict[str, tuple[int, ...]] = {}
+    for file in files:
+        with safe_open(str(file), framework="pt", device="cpu") as handle:
+            for name in handle.keys():
+                shapes[name] = tuple(handle.get_slice(name).get_shape())
+    return shapes
+
+
 def check_tensors(found: dict[str, tuple[tuple[int, ...], bool]], specs: list[TensorSpec],
                   optional: set[str] = frozenset()) -> None:
     """`found[name]` = (shape, is floating point). Raises `WeightError` unless the names are

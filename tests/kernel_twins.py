@@ -25,8 +25,13 @@ class TorchOps:
             rows = rows + position_table[positions[:out.shape[0]].long()].to(self.acc)
         out.copy_(rows.to(out.dtype))
 
-    def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out):
+    def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out, delta2=None,
+                    scale=1.0, scale2=1.0):
         d = delta.to(self.acc)
+        if delta2 is not None or scale != 1.0:
+            d = d * scale
+            if delta2 is not None:
+                d = d + delta2.to(self.acc) * scale2
         normed = d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * weight.to(self.acc)
         h.add_(normed.to(h.dtype))
         if next_weight is not None:
@@ -429,13 +434,15 @@ class TorchOps:
                 o[begin + t] = torch.einsum("hdp,hd->hp", s, q[t]).reshape(-1).to(o.dtype)
             cells[slot] = s.reshape(-1).to(cells.dtype)
 
-    def gated_group_norm(self, y, pre, gate_offset, weight, groups, eps, gate_first, out):
+    def gated_group_norm(self, y, pre, gate_offset, weight, groups, eps, gate_first, out,
+                         gate="silu"):
         """RMS norm of y in `groups` equal parts, times `weight` (as long as a row, or as a
-        part and then shared by the parts), times silu(gate) before (`gate_first`) or behind
-        the norm; gate = pre[:, gate_offset : gate_offset + width]."""
+        part and then shared by the parts), times silu(gate) (or sigmoid(gate)) before
+        (`gate_first`) or behind the norm; gate = pre[:, gate_offset : gate_offset + width]."""
         tokens, width = y.shape
+        kind = gate
         gate = pre[:, gate_offset:gate_offset + width].to(self.acc)
-        gate = gate * torch.sigmoid(gate)
+        gate = gate * torch.sigmoid(gate) if kind == "silu" else torch.sigmoid(gate)
         x = y.to(self.acc)
         if gate_first:
             x = x * gate
@@ -445,6 +452,188 @@ class TorchOps:
         if not gate_first:
             x = x * gate
         out.copy_(x.to(out.dtype))
+
+    # ---------------------------------------------------------------- stream convolution
+
+    def stream_conv(self, h, weight, state, batch, out):
+        """out_t = h_t + sum_j weight[:, j] * h_(t - taps + 1 + j) per channel, rows before the
+        step from the ring `state[slot, position % (taps - 1)]`, zeros before position 0;
+        without a weight, out = h. The ring is left as it was."""
+        tokens = h.shape[0]
+        if weight is None:
+            out.copy_(h.to(out.dtype))
+            return
+        taps = weight.shape[1]
+        ring = taps - 1
+        starts, slots, lens = batch.q_start.tolist(), batch.slots.tolist(), batch.kv_len.tolist()
+        w = weight.to(self.acc)
+        for s in range(batch.num_seqs):
+            begin, end = starts[s], starts[s + 1]
+            n = end - begin
+            if n == 0:
+                continue
+            first = lens[s] - n
+            x = h[begin:end].to(self.acc)
+            past = torch.zeros((ring, h.shape[1]), dtype=self.acc, device=h.device)
+            for k in range(1, ring + 1):                      # k tokens before the step's first
+                if first - k >= 0:
+                    past[ring - k] = state[slots[s], (first - k) % ring].to(self.acc)
+            padded = torch.cat([past, x])
+            acc = x.clone()
+            for j in range(taps):
+                acc = acc + padded[j:j + n] * w[:, j]
+            out[begin:end] = acc.to(out.dtype)
+
+    def stream_tail_store(self, h, state, batch):
+        """The rows of `h` at each sequence's last taps - 1 positions into its ring."""
+        ring = state.shape[1]
+        starts, slots, lens = batch.q_start.tolist(), batch.slots.tolist(), batch.kv_len.tolist()
+        for s in range(batch.num_seqs):
+            begin, end = starts[s], starts[s + 1]
+            first = lens[s] - (end - begin)
+            for t in range(max(begin, end - ring), end):
+                state[slots[s], (first + t - begin) % ring] = h[t].to(state.dtype)
+
+    # ---------------------------------------------------------------- rotations of pairs
+
+    def _rotate(self, x, pos, tables, pairing):
+        """x [tokens, ..., dims] rotated over all its last axis; tables (cos, sin) [positions,
+        dims / 2]."""
+        cos_t, sin_t = tables
+        shape = [x.shape[0]] + [1] * (x.dim() - 2) + [cos_t.shape[1]]
+        cos = cos_t[pos].to(self.acc).view(shape)
+        sin = sin_t[pos].to(self.acc).view(shape)
+        x = x.to(self.acc)
+        if pairing == "interleaved":
+            a, b = x[..., 0::2], x[..., 1::2]
+            return torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).flatten(-2)
+        half = x.shape[-1] // 2
+        a, b = x[..., :half], x[..., half:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+    @staticmethod
+    def _page_slots(batch, cache, tokens):
+        live = batch.seq_of_token[:tokens] >= 0
+        pos = batch.positions[:tokens].long()
+        seq = batch.seq_of_token[:tokens].long().clamp(min=0)
+        page = cache.table[seq, pos // cache.page_size].long()
+        return live & (page >= 0), page, pos % cache.page_size
+
+    def latent_prepare(self, pre, q_rank, q_norm, narrow, kv_offset, rank, down_norm, rot_dim,
+                       tables, pairing, eps, batch, cache):
+        """narrow = rmsnorm(pre[:, :q_rank]) * q_norm (if q_rank); with a cache, the row [c |
+        rotated part] of every token into its page: c = rmsnorm(pre[:, kv_offset : kv_offset +
+        rank]) * down_norm, the part pre[:, kv_offset + rank : + rot_dim] rotated."""
+        tokens = pre.shape[0]
+        if q_rank:
+            x = pre[:, :q_rank].to(self.acc)
+            narrow.copy_((x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+                          * q_norm.to(self.acc)).to(narrow.dtype))
+        if cache is None:
+            return
+        x = pre[:, kv_offset:kv_offset + rank].to(self.acc)
+        c = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * down_norm.to(self.acc)
+        pos = batch.positions[:tokens].long()
+        if rot_dim:
+            part = self._rotate(pre[:, kv_offset + rank:kv_offset + rank + rot_dim], pos, tables, pairing)
+            c = torch.cat([c, part], dim=-1)
+        keep, page, offset = self._page_slots(batch, cache, tokens)
+        cache.k[page[keep], 0, offset[keep], :] = c[keep].to(cache.k.dtype)
+
+    def rope_rows(self, q, heads, row, offset, rot_dim, tables, pairing, batch):
+        """In place: q[t, h * row + offset : + rot_dim] rotated by the token's position."""
+        tokens = q.shape[0]
+        pos = batch.positions[:tokens].long()
+        view = q.view(tokens, heads, row)[:, :, offset:offset + rot_dim]
+        view.copy_(self._rotate(view, pos, tables, pairing).to(q.dtype))
+
+    # ---------------------------------------------------------------- sigmoid attention
+
+    def qk_norm_rope_store(self, pre, layout, q_norm, k_norm, eps, tables, pairing, batch, cache, q,
+                           values_from_keys):
+        heads, kv_heads, dim, vdim = layout
+        tokens = pre.shape[0]
+        pos = batch.positions[:tokens].long()
+        qs, ks = heads * dim, kv_heads * dim
+        qx = pre[:, :qs].to(self.acc).view(tokens, heads, dim)
+        kx = pre[:, qs:qs + ks].to(self.acc).view(tokens, kv_heads, dim)
+        vx = kx if values_from_keys else pre[:, qs + ks:].to(self.acc).view(tokens, kv_heads, vdim)
+        if q_norm is not None:
+            qx = qx * torch.rsqrt(qx.pow(2).mean(-1, keepdim=True) + eps) * q_norm.to(self.acc)
+            kn = kx * torch.rsqrt(kx.pow(2).mean(-1, keepdim=True) + eps) * k_norm.to(self.acc)
+        else:
+            kn = kx
+        if tables is not None:
+            rot = 2 * tables[0].shape[1]
+            qx = torch.cat([self._rotate(qx[..., :rot], pos, tables, pairing), qx[..., rot:]], dim=-1)
+            kn = torch.cat([self._rotate(kn[..., :rot], pos, tables, pairing), kn[..., rot:]], dim=-1)
+        q.copy_(qx.reshape(tokens, qs).to(q.dtype))
+        keep, page, offset = self._page_slots(batch, cache, tokens)
+        cache.k[page[keep], :, offset[keep], :] = kn[keep].to(cache.k.dtype)
+        cache.v[page[keep], :, offset[keep], :] = vx[keep].to(cache.v.dtype)
+
+    def sigmoid_attention(self, q, layout, batch, cache, scale, window, keep_first, head_bias, out):
+        heads, kv_heads, dim, vdim = layout
+        group = heads // kv_heads
+        q_start, kv_lens = batch.q_start.tolist(), batch.kv_len.tolist()
+        ps = cache.page_size
+        for s in range(batch.num_seqs):
+            begin, end = q_start[s], q_start[s + 1]
+            q_len, kv_len = end - begin, kv_lens[s]
+            if q_len == 0:
+                continue
+            first_pos = kv_len - q_len
+            key_pos = torch.arange(kv_len, device=q.device)
+            q_pos = torch.arange(first_pos, kv_len, device=q.device)
+            seen = key_pos[None, :] <= q_pos[:, None]
+            if window > 0:
+                seen = seen & ((key_pos[None, :] > q_pos[:, None] - window)
+                               | (key_pos[None, :] < keep_first))
+            pages = cache.table[s, :-(-kv_len // ps)].long()
+            wanted = seen.any(0)
+            got = pages[key_pos // ps] >= 0
+            if bool((wanted & ~got).any()):
+                raise AssertionError("a visible key's page was given back")
+            pages = pages.clamp(min=0)
+            keys = cache.k[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, dim)[:, :kv_len]
+            vals = cache.v[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, vdim)[:, :kv_len]
+            keys = keys.to(self.acc).repeat_interleave(group, dim=0)
+            vals = vals.to(self.acc).repeat_interleave(group, dim=0)
+            vals = torch.where(wanted[None, :, None], vals, torch.zeros_like(vals))
+            keys = torch.where(wanted[None, :, None], keys, torch.zeros_like(keys))
+            qs = q[begin:end].view(q_len, heads, dim).to(self.acc)
+            scores = torch.einsum("qhd,hkd->hqk", qs, keys) * scale + head_bias.to(self.acc)[:, None, None]
+            weights = torch.sigmoid(scores) * seen[None]
+            o = torch.einsum("hqk,hkd->qhd", weights, vals)
+            out[begin:end] = o.reshape(q_len, heads * vdim).to(out.dtype)
+
+    # ---------------------------------------------------------------- generalized delta rule
+
+    def tanh_slice(self, pre, offset, count, out):
+        out.copy_(torch.tanh(pre[:, offset:offset + count].to(self.acc)).to(out.dtype))
+
+    def general_delta_scan(self, pre, offsets, decay, decay_scale, layout, unit_eps, cells, batch, o,
+                           precise=False):
+        """Per head: S <- diag(w) S - (a * u)(u^T S) + k v^T, o = S^T r with w = exp(-decay_scale
+        * sigmoid(decay)), a = sigmoid(pre[a]), u = k / sqrt(sum k^2 + unit_eps)."""
+        heads, dim, vdim = layout
+        at_r, at_k, at_v, at_a = offsets
+        keys = heads * dim
+        for begin, end, slot in self._sequences(batch):
+            rows = pre[begin:end].to(self.acc)
+            r = rows[:, at_r:at_r + keys].view(-1, heads, dim)
+            k = rows[:, at_k:at_k + keys].view(-1, heads, dim)
+            v = rows[:, at_v:at_v + heads * vdim].view(-1, heads, vdim)
+            a = torch.sigmoid(rows[:, at_a:at_a + keys]).view(-1, heads, dim)
+            w = torch.exp(-decay_scale * torch.sigmoid(decay[begin:end].to(self.acc))).view(-1, heads, dim)
+            u = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)
+            s = cells[slot].to(self.acc).view(heads, dim, vdim)
+            for t in range(end - begin):
+                us = torch.einsum("hd,hdp->hp", u[t], s)
+                s = (w[t, :, :, None] * s - (a[t] * u[t])[:, :, None] * us[:, None, :]
+                     + k[t, :, :, None] * v[t, :, None, :])
+                o[begin + t] = torch.einsum("hdp,hd->hp", s, r[t]).reshape(-1).to(o.dtype)
+            cells[slot] = s.reshape(-1).to(cells.dtype)
 
     # ---------------------------------------------------------------- latent attention
 
