@@ -159,6 +159,95 @@ int launch_head_linear(const void* x, int ld, int offset, const void* w, void* o
     return launch_status();
 }
 
+
+// A pair of numbers turned by the angle of (position, pair i): (u, v) -> (u cos - v sin, v cos +
+// u sin); cos_t and sin_t are [positions][pairs].
+__device__ __forceinline__ void turn_pair(float& u, float& v, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, int pos, int pairs, int i) {
+    const float c = cos_t[(int64_t)pos * pairs + i], s = sin_t[(int64_t)pos * pairs + i];
+    const float a = u * c - v * s, b = v * c + u * s;
+    u = a;
+    v = b;
+}
+
+// What stands in front of latent attention with a query latent and a rotated key part shared
+// by the heads. A warp per token, float32 arithmetic:
+//   narrow[t] = rmsnorm(pre[t][0 .. q_rank)) * wq                         (if q_rank > 0)
+//   page row of t = [rmsnorm(pre[t][kv .. kv + rank)) * wc | rot(pre[t][kv + rank .. + rot_dim))]
+//                                                                       (if pages are given)
+// The rotation pairs neighbours (2i, 2i + 1) when `interleaved`, else i with i + rot_dim / 2.
+template <typename T>
+__global__ void latent_prepare_kernel(const float* __restrict__ pre, int ld, int q_rank,
+                                      const void* __restrict__ wq, T* __restrict__ narrow,
+                                      int kv, int rank, const void* __restrict__ wc, int w_dtype,
+                                      int rot_dim, const float* __restrict__ cos_t,
+                                      const float* __restrict__ sin_t, int interleaved, float eps,
+                                      const int* __restrict__ positions,
+                                      const int* __restrict__ seq_of_token,
+                                      const int* __restrict__ table, int max_pages,
+                                      T* __restrict__ pages, int page_size, int tokens) {
+    grid_dependency_sync();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const int seq = seq_of_token[t];
+    const float* row = pre + (int64_t)t * ld;
+    if (q_rank > 0) {
+        float ss = 0.f;
+        if (seq >= 0)
+            for (int c = lane; c < q_rank; c += 32) ss = fmaf(row[c], row[c], ss);
+        ss = warp_sum(ss);
+        const float rstd = 1.f / sqrtf(ss / (float)q_rank + eps);
+        for (int c = lane; c < q_rank; c += 32)
+            narrow[(int64_t)t * q_rank + c] =
+                from_float<T>(seq >= 0 ? row[c] * rstd * load_as_float(wq, c, w_dtype) : 0.f);
+    }
+    if (pages == nullptr || seq < 0) return;
+    const int pos = positions[t];
+    const int page = table_page(table, seq, max_pages, pos / page_size);
+    if (page < 0) return;
+    const float* x = row + kv;
+    float ss = 0.f;
+    for (int c = lane; c < rank; c += 32) ss = fmaf(x[c], x[c], ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / (float)rank + eps);
+    T* to = pages + ((int64_t)page * page_size + (pos % page_size)) * (rank + rot_dim);
+    for (int c = lane; c < rank; c += 32)
+        to[c] = from_float<T>(x[c] * rstd * load_as_float(wc, c, w_dtype));
+    const int pairs = rot_dim / 2, at = checked_position(pos);
+    for (int i = lane; i < pairs; i += 32) {
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + pairs;
+        float u = x[rank + a], v = x[rank + b];
+        turn_pair(u, v, cos_t, sin_t, at, pairs, i);
+        to[rank + a] = from_float<T>(u);
+        to[rank + b] = from_float<T>(v);
+    }
+}
+
+// In place: the rot_dim numbers from column `offset` of every head's row of q [tokens][heads *
+// row] turned by the token's position. A thread per (token, head, pair).
+template <typename T>
+__global__ void rope_rows_kernel(T* __restrict__ q, int heads, int row, int offset, int rot_dim,
+                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                 int interleaved, const int* __restrict__ positions,
+                                 const int* __restrict__ seq_of_token, int tokens) {
+    grid_dependency_sync();
+    const int pairs = rot_dim / 2;
+    const int64_t id = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (int64_t)tokens * heads * pairs) return;
+    const int i = (int)(id % pairs);
+    const int h = (int)((id / pairs) % heads);
+    const int t = (int)(id / ((int64_t)pairs * heads));
+    if (seq_of_token[t] < 0) return;
+    const int pos = checked_position(positions[t]);
+    T* at = q + ((int64_t)t * heads + h) * row + offset;
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + pairs;
+    float u = to_float(at[a]), v = to_float(at[b]);
+    turn_pair(u, v, cos_t, sin_t, pos, pairs, i);
+    at[a] = from_float<T>(u);
+    at[b] = from_float<T>(v);
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -202,4 +291,52 @@ MB_EXPORT int mb_head_linear(const void* x, int x_dtype, int ld, int offset, con
         case 1: return launch_head_linear<float, float, bf>(x, ld, offset, w, out, tokens, heads, in, outs, s);
     }
     return MB_ERR_BAD_DTYPE;
+}
+
+// dtype: the type of `narrow` and of the pages (MB_F32 or MB_BF16); w_dtype: the type of both
+// norm weights. q_rank 0: no query latent; pages null: the layer stores no rows; rot_dim 0: no
+// rotated part (cos_t and sin_t may then be null).
+MB_EXPORT int mb_latent_prepare(const float* pre, int ld, int q_rank, const void* wq, void* narrow,
+                                int kv, int rank, const void* wc, int w_dtype, int rot_dim,
+                                const float* cos_t, const float* sin_t, int interleaved, float eps,
+                                const int* positions, const int* seq_of_token, const int* table,
+                                int max_pages, void* pages, int page_size, int tokens, int dtype,
+                                void* stream) {
+    if (tokens <= 0) return MB_OK;
+    if (q_rank < 0 || rot_dim < 0 || (rot_dim & 1)) return MB_ERR_UNSUPPORTED_SIZE;
+    if (pages != nullptr && (rank <= 0 || page_size <= 0 || (rot_dim > 0 && (!cos_t || !sin_t))))
+        return MB_ERR_UNSUPPORTED_SIZE;
+    const int blocks = (tokens + 3) / 4;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        MB_LAUNCH((latent_prepare_kernel<float>), blocks, 128, 0, s, pre, ld, q_rank, wq, (float*)narrow,
+                  kv, rank, wc, w_dtype, rot_dim, cos_t, sin_t, interleaved, eps, positions,
+                  seq_of_token, table, max_pages, (float*)pages, page_size, tokens);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH((latent_prepare_kernel<__nv_bfloat16>), blocks, 128, 0, s, pre, ld, q_rank, wq,
+                  (__nv_bfloat16*)narrow, kv, rank, wc, w_dtype, rot_dim, cos_t, sin_t, interleaved, eps,
+                  positions, seq_of_token, table, max_pages, (__nv_bfloat16*)pages, page_size, tokens);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+MB_EXPORT int mb_rope_rows(void* q, int dtype, int heads, int row, int offset, int rot_dim,
+                           const float* cos_t, const float* sin_t, int interleaved,
+                           const int* positions, const int* seq_of_token, int tokens, void* stream) {
+    if (tokens <= 0 || rot_dim <= 0) return MB_OK;
+    if ((rot_dim & 1) || offset < 0 || offset + rot_dim > row || heads <= 0) return MB_ERR_UNSUPPORTED_SIZE;
+    const long long total = (long long)tokens * heads * (rot_dim / 2);
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return MB_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MB_F32)
+        MB_LAUNCH((rope_rows_kernel<float>), (int)blocks, 256, 0, s, (float*)q, heads, row, offset,
+                  rot_dim, cos_t, sin_t, interleaved, positions, seq_of_token, tokens);
+    else if (dtype == MB_BF16)
+        MB_LAUNCH((rope_rows_kernel<__nv_bfloat16>), (int)blocks, 256, 0, s, (__nv_bfloat16*)q, heads,
+                  row, offset, rot_dim, cos_t, sin_t, interleaved, positions, seq_of_token, tokens);
+    else
+        return MB_ERR_BAD_DTYPE;
+    return launch_status();
 }

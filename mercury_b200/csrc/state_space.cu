@@ -35,6 +35,9 @@ constexpr int SS_SLICES = 8;     // lanes that share a column
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float gate_f(float x, bool sigmoid) {
+    return sigmoid ? 1.f / (1.f + expf(-x)) : silu_f(x);
+}
 
 // One float from global to shared memory without passing through registers (zeros when
 // `take` is false), and the waits that go with it: the scans fetch the next tile of tokens
@@ -606,9 +609,156 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
     }
 }
 
+// ---- generalized delta rule --------------------------------------------------------------------
+// pre: [tokens][ld] float32 with r, k (heads * dim each), v (heads * vdim) and the raw removal
+// rates a (heads * dim) at the given column offsets; decay_in: [tokens][heads * dim] raw decay
+// inputs. Per head, with u = k / sqrt(sum k^2 + unit_eps), a = sigmoid(raw a) and w = exp(-
+// decay_scale * sigmoid(raw decay)) per key channel:
+//   S <- diag(w) S - (a * u) (u^T S) + k v^T,   o = S^T r,
+// both terms reading the matrix as the token found it (A). Column p of S needs two sums over
+// A's rows, x = u . A[:, p] and y = (w * r) . A[:, p]; then S[:, p] = w * A[:, p] - (a * u) x + k
+// v_p and o_p = y - x ((a * u) . r) + v_p (k . r): one pass over the column per token. S is
+// [dim][vdim] at cells[slot][(head * dim + d) * vdim + p]. The split of a head over lanes is the
+// one described at the top of this file (eight lanes a column, four neighbouring rows at a
+// time). The decay is computed in double and rounded once.
+template <int DPT, typename S>
+__global__ void __launch_bounds__(512)
+general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int at_k, int at_v, int at_a,
+                          const float* __restrict__ decay_in, float decay_scale, float unit_eps,
+                          float* __restrict__ cells, int64_t cell_stride,
+                          const int* __restrict__ q_start, const int* __restrict__ slots,
+                          float* __restrict__ out, int heads, int dim, int vdim, int chunks_per_head) {
+    grid_dependency_sync();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int SL = SS_SLICES;
+    constexpr int DP = DPT * SL;
+    const int cols = (blockDim.x >> 5) * (32 / SL);
+    float* wr_s = sm;                          // r, then w * r    [SS_TILE][DP]
+    float* k_s = wr_s + SS_TILE * DP;          // k
+    float* au_s = k_s + SS_TILE * DP;          // raw a, then a * u
+    float* w_s = au_s + SS_TILE * DP;          // raw decay, then w
+    float* u_s = w_s + SS_TILE * DP;           // u
+    float* v_s = u_s + SS_TILE * DP;           // [SS_TILE][cols]
+    __shared__ float aur_s[SS_TILE], kr_s[SS_TILE];
+    const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], end = q_start[seq + 1];
+    if (begin >= end) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    const int slice = lane & (SL - 1), p_local = warp * (32 / SL) + lane / SL;
+    const int p = chunk * cols + p_local;
+    const bool live = p < vdim;
+    const int inner = heads * vdim;
+    float* mine = cells + (int64_t)slots[seq] * cell_stride + (int64_t)head * dim * vdim;
+    S s[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = row_in<SL>(slice, i);
+        s[i] = (live && d < dim) ? (S)mine[(int64_t)d * vdim + p] : (S)0;
+    }
+    for (int t0 = begin; t0 < end; t0 += SS_TILE) {
+        const int nt = min(SS_TILE, end - t0);
+        for (int idx = tid; idx < nt * DP; idx += blockDim.x) {
+            const int tt = idx / DP, d = idx - tt * DP;
+            const bool take = d < dim;
+            const float* row = pre + (int64_t)(t0 + tt) * ld + head * dim + d;
+            wr_s[idx] = take ? row[at_r] : 0.f;
+            k_s[idx] = take ? row[at_k] : 0.f;
+            au_s[idx] = take ? row[at_a] : 0.f;
+            w_s[idx] = take ? decay_in[(int64_t)(t0 + tt) * heads * dim + head * dim + d] : 0.f;
+        }
+        for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
+            const int tt = idx / cols, pp = chunk * cols + (idx - tt * cols);
+            v_s[idx] = pp < vdim ? pre[(int64_t)(t0 + tt) * ld + at_v + head * vdim + pp] : 0.f;
+        }
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += warps) {
+            float kk = 0.f;
+            for (int d = lane; d < dim; d += 32) kk = fmaf(k_s[tt * DP + d], k_s[tt * DP + d], kk);
+            kk = warp_sum(kk);
+            const float rk = 1.f / sqrtf(kk + unit_eps);
+            float aur = 0.f, kr = 0.f;
+            for (int d = lane; d < dim; d += 32) {
+                const int at = tt * DP + d;
+                const float r = wr_s[at], k = k_s[at];
+                const float u = k * rk;
+                const float a = 1.f / (1.f + expf(-au_s[at]));
+                const float w = (float)exp(-(double)decay_scale / (1.0 + exp(-(double)w_s[at])));
+                u_s[at] = u;
+                au_s[at] = a * u;
+                w_s[at] = w;
+                wr_s[at] = w * r;
+                aur = fmaf(a * u, r, aur);
+                kr = fmaf(k, r, kr);
+            }
+            aur = warp_sum(aur);
+            kr = warp_sum(kr);
+            if (lane == 0) {
+                aur_s[tt] = aur;
+                kr_s[tt] = kr;
+            }
+            // rows beyond dim stay as staged: zero everywhere, so padded rows of S stay zero
+            for (int d = dim + lane; d < DP; d += 32) u_s[tt * DP + d] = 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float4* ut = reinterpret_cast<const float4*>(u_s + tt * DP) + slice;
+            const float4* yt = reinterpret_cast<const float4*>(wr_s + tt * DP) + slice;
+            S px[4] = {(S)0, (S)0, (S)0, (S)0}, py[4] = {(S)0, (S)0, (S)0, (S)0};
+#pragma unroll
+            for (int j = 0; j < DPT / 4; ++j) {
+                const float4 uv = ut[SL * j], yv = yt[SL * j];
+                px[0] = fma(s[4 * j], (S)uv.x, px[0]);
+                px[1] = fma(s[4 * j + 1], (S)uv.y, px[1]);
+                px[2] = fma(s[4 * j + 2], (S)uv.z, px[2]);
+                px[3] = fma(s[4 * j + 3], (S)uv.w, px[3]);
+                py[0] = fma(s[4 * j], (S)yv.x, py[0]);
+                py[1] = fma(s[4 * j + 1], (S)yv.y, py[1]);
+                py[2] = fma(s[4 * j + 2], (S)yv.z, py[2]);
+                py[3] = fma(s[4 * j + 3], (S)yv.w, py[3]);
+            }
+            const S x = lanes_sum<SL, S>((px[0] + px[1]) + (px[2] + px[3]));
+            const S y = lanes_sum<SL, S>((py[0] + py[1]) + (py[2] + py[3]));
+            const S vp = (S)v_s[tt * cols + p_local];
+            const float4* wt = reinterpret_cast<const float4*>(w_s + tt * DP) + slice;
+            const float4* at = reinterpret_cast<const float4*>(au_s + tt * DP) + slice;
+            const float4* kt = reinterpret_cast<const float4*>(k_s + tt * DP) + slice;
+#pragma unroll
+            for (int j = 0; j < DPT / 4; ++j) {
+                const float4 wv = wt[SL * j], av = at[SL * j], kv = kt[SL * j];
+                s[4 * j] = fma((S)wv.x, s[4 * j], fma((S)kv.x, vp, -(S)av.x * x));
+                s[4 * j + 1] = fma((S)wv.y, s[4 * j + 1], fma((S)kv.y, vp, -(S)av.y * x));
+                s[4 * j + 2] = fma((S)wv.z, s[4 * j + 2], fma((S)kv.z, vp, -(S)av.z * x));
+                s[4 * j + 3] = fma((S)wv.w, s[4 * j + 3], fma((S)kv.w, vp, -(S)av.w * x));
+            }
+            if (slice == 0 && live)
+                out[(int64_t)(t0 + tt) * inner + head * vdim + p] =
+                    (float)(y - x * (S)aur_s[tt] + vp * (S)kr_s[tt]);
+        }
+        __syncthreads();                      // the tile may be refilled
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = row_in<SL>(slice, i);
+        if (live && d < dim) mine[(int64_t)d * vdim + p] = (float)s[i];
+    }
+}
+
+// out[t][c] = tanh(pre[t][offset + c]), float32.
+__global__ void tanh_slice_kernel(const float* __restrict__ pre, int ld, int offset, int count,
+                                  float* __restrict__ out, int64_t total) {
+    grid_dependency_sync();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / count;
+        out[i] = tanhf(pre[t * ld + offset + (i - t * count)]);
+    }
+}
+
 // ---- gated group norm ------------------------------------------------------------------------
-// y: [tokens][width] float32 in `groups` equal parts; gate = silu(pre[:, gate_offset + c]).
-// gate_first: out = rmsnorm_part(y * gate) * w;  else: out = rmsnorm_part(y) * w * gate.
+// y: [tokens][width] float32 in `groups` equal parts; gate = silu(pre[:, gate_offset + c]), or
+// sigmoid(.) when bit 1 of `gate_first` is set. Bit 0 of gate_first: out = rmsnorm_part(y * gate)
+// * w;  else: out = rmsnorm_part(y) * w * gate.
 // w has `wn` entries and is read at c % wn (one weight per feature, or one per feature of a
 // part, shared by the parts). A warp per (token, part).
 template <typename TO>
@@ -624,21 +774,22 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     const int width = groups * size;
     const float* yr = y + (int64_t)t * width + part * size;
     const float* gr = pre + (int64_t)t * pre_ld + gate_offset + part * size;
+    const bool first = gate_first & 1, sig = gate_first & 2;
     float ss = 0.f;
     for (int c = lane; c < size; c += 32) {
         float x = yr[c];
-        if (gate_first) x *= silu_f(gr[c]);
+        if (first) x *= gate_f(gr[c], sig);
         ss = fmaf(x, x, ss);
     }
     ss = warp_sum(ss);
     const float rstd = 1.f / sqrtf(ss / (float)size + eps);
     TO* orow = out + (int64_t)t * width + part * size;
     for (int c = lane; c < size; c += 32) {
-        const float gate = silu_f(gr[c]);
+        const float gate = gate_f(gr[c], sig);
         float x = yr[c];
-        if (gate_first) x *= gate;
+        if (first) x *= gate;
         x = x * rstd * w[(part * size + c) % wn];
-        if (!gate_first) x *= gate;
+        if (!first) x *= gate;
         orow[c] = from_float<TO>(x);
     }
 }
@@ -656,21 +807,22 @@ gated_group_norm_block_kernel(const float* __restrict__ y, const float* __restri
     const int width = groups * size;
     const float* yr = y + (int64_t)t * width + part * size;
     const float* gr = pre + (int64_t)t * pre_ld + gate_offset + part * size;
+    const bool first = gate_first & 1, sig = gate_first & 2;
     float ss = 0.f;
     for (int c = threadIdx.x; c < size; c += blockDim.x) {
         float x = yr[c];
-        if (gate_first) x *= silu_f(gr[c]);
+        if (first) x *= gate_f(gr[c], sig);
         ss = fmaf(x, x, ss);
     }
     ss = block_sum(ss, scratch);
     const float rstd = 1.f / sqrtf(ss / (float)size + eps);
     TO* orow = out + (int64_t)t * width + part * size;
     for (int c = threadIdx.x; c < size; c += blockDim.x) {
-        const float gate = silu_f(gr[c]);
+        const float gate = gate_f(gr[c], sig);
         float x = yr[c];
-        if (gate_first) x *= gate;
+        if (first) x *= gate;
         x = x * rstd * w[(part * size + c) % wn];
-        if (!gate_first) x *= gate;
+        if (!first) x *= gate;
         orow[c] = from_float<TO>(x);
     }
 }
@@ -905,6 +1057,56 @@ MB_EXPORT int mb_delta_rule_scan(const float* qkv, const float* pre, int pre_ld,
     else if (dim <= 128) MB_DR_CASE(16);
     else MB_DR_CASE(32);
 #undef MB_DR_CASE
+    return launch_status();
+}
+
+// The generalized delta rule over a step's tokens; `precise`: the matrices are held in double
+// while the step runs. Key sizes up to 256.
+MB_EXPORT int mb_general_delta_scan(const float* pre, int ld, int at_r, int at_k, int at_v, int at_a,
+                                    const float* decay_in, float decay_scale, float unit_eps,
+                                    float* cells, long long cell_stride, const int* q_start,
+                                    const int* slots, float* out, int num_seqs, int heads, int dim,
+                                    int vdim, int precise, void* stream) {
+    if (num_seqs <= 0 || heads <= 0) return MB_OK;
+    if (dim <= 0 || dim > 256 || vdim <= 0 || num_seqs > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    int warps = (vdim + 3) / 4;
+    if (warps < 4) warps = 4;
+    if (warps > 16) warps = 16;
+    const int cols = warps * 4;
+    const int chunks = (vdim + cols - 1) / cols;
+    dim3 grid(heads * chunks, num_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+#define MB_GD_CASE(DPT)                                                                            \
+    do {                                                                                           \
+        const size_t smem = (size_t)(5 * SS_TILE * DPT * SS_SLICES + SS_TILE * cols) * sizeof(float); \
+        if (!allow_smem(general_delta_scan_kernel<DPT, double>, smem) ||                           \
+            !allow_smem(general_delta_scan_kernel<DPT, float>, smem))                              \
+            return MB_ERR_UNSUPPORTED_SIZE;                                                        \
+        if (precise)                                                                               \
+            MB_LAUNCH((general_delta_scan_kernel<DPT, double>), grid, warps * 32, smem, s, pre, ld, \
+                      at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,              \
+                      (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks);        \
+        else                                                                                       \
+            MB_LAUNCH((general_delta_scan_kernel<DPT, float>), grid, warps * 32, smem, s, pre, ld, \
+                      at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,              \
+                      (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks);        \
+    } while (0)
+    if (dim <= 32) MB_GD_CASE(4);
+    else if (dim <= 64) MB_GD_CASE(8);
+    else if (dim <= 128) MB_GD_CASE(16);
+    else MB_GD_CASE(32);
+#undef MB_GD_CASE
+    return launch_status();
+}
+
+MB_EXPORT int mb_tanh_slice(const float* pre, int ld, int offset, int count, float* out, int tokens,
+                            void* stream) {
+    const long long total = (long long)tokens * count;
+    if (total <= 0) return MB_OK;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+    MB_LAUNCH((tanh_slice_kernel), blocks, 256, 0, (cudaStream_t)stream, pre, ld, offset, count, out,
+              (int64_t)total);
     return launch_status();
 }
 

@@ -1,7 +1,8 @@
-// Operations on the float32 residual stream and the logits that the pre-norm blocks with a
-// layer scale use: an embedding lookup with a constant factor, the residual sum under a
-// per-feature scale fused with the norm that follows (layer norm or RMS norm), and the soft
-// cap of the logits. All arithmetic is float32.
+// Operations on the float32 residual stream and the logits: an embedding lookup with a
+// constant factor, the residual sum under a per-feature scale fused with the norm that follows
+// (layer norm or RMS norm), the soft cap of the logits, the norm behind two sublayers that ran
+// side by side, and the short causal convolution of the stream that a sublayer may read in
+// place of the stream. All arithmetic is float32.
 #include "common.cuh"
 
 namespace mb {
@@ -74,6 +75,95 @@ __global__ void softcap_kernel(float* __restrict__ x, int64_t total, float cap) 
         x[i] = cap * tanhf(x[i] * inv);
 }
 
+
+// A norm BEHIND two sublayers that ran side by side: d = a * delta + b * delta2 (delta2 may be
+// null), h <- h + d * rsqrt(mean(d^2) + eps) * w. One block per row, d kept in shared memory.
+template <typename TD>
+__global__ void rmsnorm_add_pair_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                        const TD* __restrict__ delta2, float a, float b,
+                                        const void* __restrict__ w, int w_dtype, float eps,
+                                        int hidden) {
+    grid_dependency_sync();
+    extern __shared__ float pair_row_s[];
+    __shared__ float scratch[33];
+    const int64_t at = (int64_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float d = a * to_float(delta[at + c]);
+        if (delta2 != nullptr) d = fmaf(b, to_float(delta2[at + c]), d);
+        pair_row_s[c] = d;
+        ss = fmaf(d, d, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.f / sqrtf(ss / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        h[at + c] += pair_row_s[c] * rstd * load_as_float(w, c, w_dtype);
+}
+
+// What a sublayer reads in place of the stream: out[t][c] = x[t][c] + sum_j w[c][j] *
+// x(p - taps + 1 + j)[c], where x(q) is the stream's row at position q of the token's
+// sequence: zero for q < 0, a row of this step for q >= first (the position of the
+// sequence's first token in this step), else ring[slot][q % (taps - 1)], the rows that
+// earlier steps left. The ring is not changed here. w null: out = x. A thread per (token,
+// channel); float32 arithmetic, j ascending, so a token's sum does not depend on the cut.
+template <typename TO>
+__global__ void stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, int taps,
+                                   const float* __restrict__ ring, int64_t ring_stride,
+                                   const int* __restrict__ positions,
+                                   const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ q_start, const int* __restrict__ kv_len,
+                                   const int* __restrict__ slots, TO* __restrict__ out, int tokens,
+                                   int hidden) {
+    grid_dependency_sync();
+    const int t = blockIdx.y;
+    const int seq = seq_of_token[t];
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= hidden) return;
+    if (seq < 0) {
+        out[(int64_t)t * hidden + c] = from_float<TO>(0.f);
+        return;
+    }
+    const float own = x[(int64_t)t * hidden + c];
+    if (w == nullptr) {
+        out[(int64_t)t * hidden + c] = from_float<TO>(own);
+        return;
+    }
+    const int pos = positions[t];
+    const int first = kv_len[seq] - (q_start[seq + 1] - q_start[seq]);
+    const int span = taps - 1;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = span - j;                 // how many tokens before this one
+        const int q = pos - back;
+        float v = 0.f;
+        if (back == 0) v = own;
+        else if (q >= first) v = x[(int64_t)(t - back) * hidden + c];
+        else if (q >= 0) v = ring[(int64_t)slots[seq] * ring_stride + (int64_t)(q % span) * hidden + c];
+        acc = fmaf(w[(int64_t)c * taps + j], v, acc);
+    }
+    out[(int64_t)t * hidden + c] = from_float<TO>(own + acc);
+}
+
+// After the step's convolutions: the stream's rows at each sequence's last taps - 1
+// positions of this step into its ring, row of position q at q % (taps - 1).
+__global__ void stream_tail_store_kernel(const float* __restrict__ x, float* __restrict__ ring,
+                                         int64_t ring_stride, int span,
+                                         const int* __restrict__ q_start,
+                                         const int* __restrict__ kv_len,
+                                         const int* __restrict__ slots, int hidden) {
+    grid_dependency_sync();
+    const int seq = blockIdx.y;
+    const int begin = q_start[seq], end = q_start[seq + 1];
+    const int back = blockIdx.z + 1;               // the back-th token from the step's end
+    if (end - begin < back) return;
+    const int t = end - back;
+    const int pos = kv_len[seq] - back;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= hidden) return;
+    ring[(int64_t)slots[seq] * ring_stride + (int64_t)(pos % span) * hidden + c] =
+        x[(int64_t)t * hidden + c];
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -126,5 +216,76 @@ MB_EXPORT int mb_softcap(float* x, long long total, float cap, void* stream) {
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
     MB_LAUNCH((softcap_kernel), blocks, 256, 0, (cudaStream_t)stream, x, (int64_t)total, cap);
+    return launch_status();
+}
+
+// delta2 may be null (then b is not used); both deltas share `delta_dtype`.
+MB_EXPORT int mb_rmsnorm_add_pair(float* h, const void* delta, const void* delta2, int delta_dtype,
+                                  float a, float b, const void* w, int w_dtype, float eps, int count,
+                                  int hidden, void* stream) {
+    if (count <= 0 || hidden <= 0) return MB_OK;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 160 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define MB_RAP_CASE(TD)                                                                           \
+    do {                                                                                          \
+        static size_t raised = 0;                                                                 \
+        if (smem > 48 * 1024 && smem > raised) {                                                  \
+            if (cudaFuncSetAttribute(rmsnorm_add_pair_kernel<TD>,                                 \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=   \
+                cudaSuccess)                                                                      \
+                return MB_ERR_UNSUPPORTED_SIZE;                                                   \
+            raised = smem;                                                                        \
+        }                                                                                         \
+        MB_LAUNCH((rmsnorm_add_pair_kernel<TD>), count, threads, smem, s, h, (const TD*)delta,    \
+                  (const TD*)delta2, a, b, w, w_dtype, eps, hidden);                              \
+    } while (0)
+    if (delta_dtype == MB_F32) MB_RAP_CASE(float);
+    else if (delta_dtype == MB_BF16) MB_RAP_CASE(bf);
+    else return MB_ERR_BAD_DTYPE;
+#undef MB_RAP_CASE
+    return launch_status();
+}
+
+// w: [hidden][taps] float32 or null (out = x); ring: [slots][taps - 1][hidden] float32 with
+// `ring_stride` floats between two slots (null when taps is 1). out_dtype: MB_F32 or MB_BF16.
+MB_EXPORT int mb_stream_conv(const float* x, const float* w, int taps, const float* ring,
+                             long long ring_stride, const int* positions, const int* seq_of_token,
+                             const int* q_start, const int* kv_len, const int* slots, void* out,
+                             int out_dtype, int tokens, int hidden, void* stream) {
+    if (tokens <= 0 || hidden <= 0) return MB_OK;
+    if (w != nullptr && (taps < 1 || (taps > 1 && ring == nullptr))) return MB_ERR_UNSUPPORTED_SIZE;
+    if (tokens > 65535 * 16) return MB_ERR_UNSUPPORTED_SIZE;
+    const int threads = hidden >= 256 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int t0 = 0; t0 < tokens; t0 += 65535) {
+        const int n = tokens - t0 < 65535 ? tokens - t0 : 65535;
+        dim3 grid((hidden + threads - 1) / threads, n);
+        const float* xs = x + (int64_t)t0 * hidden;
+        if (out_dtype == MB_F32)
+            MB_LAUNCH((stream_conv_kernel<float>), grid, threads, 0, s, xs, w, taps, ring,
+                      (int64_t)ring_stride, positions + t0, seq_of_token + t0, q_start, kv_len, slots,
+                      (float*)out + (int64_t)t0 * hidden, n, hidden);
+        else if (out_dtype == MB_BF16)
+            MB_LAUNCH((stream_conv_kernel<__nv_bfloat16>), grid, threads, 0, s, xs, w, taps, ring,
+                      (int64_t)ring_stride, positions + t0, seq_of_token + t0, q_start, kv_len, slots,
+                      (__nv_bfloat16*)out + (int64_t)t0 * hidden, n, hidden);
+        else
+            return MB_ERR_BAD_DTYPE;
+    }
+    return launch_status();
+}
+
+MB_EXPORT int mb_stream_tail_store(const float* x, float* ring, long long ring_stride, int span,
+                                   const int* q_start, const int* kv_len, const int* slots,
+                                   int num_seqs, int hidden, void* stream) {
+    if (num_seqs <= 0 || hidden <= 0 || span <= 0) return MB_OK;
+    if (num_seqs > 65535 || span > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    const int threads = hidden >= 256 ? 256 : 128;
+    dim3 grid((hidden + threads - 1) / threads, num_seqs, span);
+    MB_LAUNCH((stream_tail_store_kernel), grid, threads, 0, (cudaStream_t)stream, x, ring,
+              (int64_t)ring_stride, span, q_start, kv_len, slots, hidden);
     return launch_status();
 }

@@ -144,6 +144,27 @@ _SIGNATURES = {
     "mb_expert_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_expert_combine_sorted": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_expert_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_rmsnorm_add_pair": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int,
+                            c_float, c_int, c_int, c_void_p],
+    "mb_stream_conv": [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_stream_tail_store": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                             c_int, c_void_p],
+    "mb_latent_prepare": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
+                          c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                          c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "mb_rope_rows": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                     c_void_p, c_int, c_void_p],
+    "mb_qk_norm_rope_store": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                              c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_sigmoid_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_general_delta_scan": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float,
+                              c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_int, c_int, c_void_p],
+    "mb_tanh_slice": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "mb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "mb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
@@ -191,6 +212,8 @@ def load():
     lib.mb_mixed_head_scratch_floats.restype = c_longlong
     lib.mb_mamba2_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int]
     lib.mb_mamba2_scratch_floats.restype = c_longlong
+    lib.mb_sigmoid_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mb_sigmoid_attention_scratch_floats.restype = c_longlong
     _LIB = lib
     return lib
 

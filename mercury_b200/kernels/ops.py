@@ -302,10 +302,27 @@ class CudaOps:
         self._note_stream_write()
 
     @_timed("norm")
-    def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out):
+    def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out, delta2=None,
+                    scale=1.0, scale2=1.0):
         """h += rmsnorm(delta) * weight (a norm behind a sublayer); with `next_weight` also
-        out = rmsnorm(h) * next_weight of the new stream, in the same kernel."""
+        out = rmsnorm(h) * next_weight of the new stream, in the same kernel. With `delta2` or a
+        `scale` the norm is taken of scale * delta + scale2 * delta2 (two sublayers that ran
+        side by side)."""
         self._rows(h), self._rows(delta)
+        if delta2 is not None or scale != 1.0:
+            if next_weight is not None:
+                raise KernelError("rmsnorm_add: two deltas together with the next norm are not built")
+            if delta2 is not None:
+                self._rows(delta2)
+                if delta2.dtype != delta.dtype or delta2.shape != delta.shape:
+                    raise KernelError("rmsnorm_add: the two deltas differ in type or shape")
+            check(self.lib.mb_rmsnorm_add_pair(
+                _ptr(h), _ptr(delta), _ptr(delta2), _flag(delta.dtype), float(scale), float(scale2),
+                _ptr(weight), _flag(weight.dtype), float(eps), h.shape[0], h.shape[1],
+                self._stream()), "rmsnorm_add (pair)")
+            self.launches += 1
+            self._note_stream_write()
+            return
         check(self.lib.mb_rmsnorm_add(
             _ptr(h), _ptr(delta), _flag(delta.dtype), _ptr(weight), _flag(weight.dtype), float(eps),
             _ptr(next_weight), _flag(next_weight.dtype) if next_weight is not None else 0,
@@ -726,15 +743,131 @@ class CudaOps:
         self.launches += 1
 
     @_timed("recurrence")
-    def gated_group_norm(self, y, pre, gate_offset, weight, groups, eps, gate_first, out):
+    def gated_group_norm(self, y, pre, gate_offset, weight, groups, eps, gate_first, out,
+                         gate="silu"):
         """RMS norm of y (float32) in `groups` equal parts times `weight` (read at c modulo its
-        length), times silu(pre[:, gate_offset + c]) before (`gate_first`) or behind the norm."""
+        length), times silu(pre[:, gate_offset + c]) (`gate` "sigmoid": sigmoid(.)) before
+        (`gate_first`) or behind the norm."""
         tokens, width = y.shape
+        if gate not in ("silu", "sigmoid"):
+            raise KernelError(f"gated_group_norm: no gate {gate!r}")
+        flags = int(bool(gate_first)) | (2 if gate == "sigmoid" else 0)
         check(self.lib.mb_gated_group_norm(
             _ptr(y), _ptr(pre), pre.shape[1], int(gate_offset), _ptr(weight), weight.numel(),
-            int(groups), width // int(groups), float(eps), int(bool(gate_first)), _ptr(out),
+            int(groups), width // int(groups), float(eps), flags, _ptr(out),
             _flag(out.dtype), tokens, self._stream()), "gated_group_norm")
         self.launches += 1
+
+    # ------------------------------------------------------------------ generalized delta rule
+
+    @_timed("recurrence")
+    def tanh_slice(self, pre, offset, count, out):
+        """out = tanh(pre[:, offset : offset + count]), float32."""
+        check(self.lib.mb_tanh_slice(_ptr(pre), pre.shape[1], int(offset), int(count), _ptr(out),
+                                     pre.shape[0], self._stream()), "tanh_slice")
+        self.launches += 1
+
+    @_timed("recurrence")
+    def general_delta_scan(self, pre, offsets, decay, decay_scale, layout, unit_eps, cells, batch, o,
+                           precise=False):
+        """Per head S <- diag(w) S - (a * u)(u^T S) + k v^T, o = S^T r, with w = exp(-decay_scale *
+        sigmoid(decay)), a = sigmoid(pre[a]) and u = k / sqrt(sum k^2 + unit_eps); r, k, v and a
+        are read off `pre` at `offsets`; `cells` [slots, heads * dim * vdim] holds the matrices;
+        everything float32 (`precise` as in `mamba2_scan`)."""
+        heads, dim, vdim = layout
+        at_r, at_k, at_v, at_a = offsets
+        if pre.dtype != torch.float32 or decay.dtype != torch.float32 or o.dtype != torch.float32:
+            raise KernelError("general_delta_scan: inputs and read-outs are float32")
+        check(self.lib.mb_general_delta_scan(
+            _ptr(pre), pre.shape[1], int(at_r), int(at_k), int(at_v), int(at_a), _ptr(decay),
+            float(decay_scale), float(unit_eps), _ptr(cells), cells.stride(0), _ptr(batch.q_start),
+            _ptr(batch.slots), _ptr(o), batch.num_seqs, heads, dim, vdim, int(bool(precise)),
+            self._stream()), "general_delta_scan")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ stream convolution
+
+    @_timed("norm")
+    def stream_conv(self, h, weight, state, batch, out):
+        """out = h + the causal convolution of h per channel (weight [hidden, taps] float32),
+        rows from before the step out of the ring `state` [slots, taps - 1, hidden]; without a
+        weight out = h. The ring is left as it was."""
+        self._rows(h), self._rows(out)
+        taps = weight.shape[1] if weight is not None else 1
+        if weight is not None and (weight.dtype != torch.float32 or not weight.is_contiguous()):
+            raise KernelError("stream_conv: the taps are a contiguous float32 matrix")
+        check(self.lib.mb_stream_conv(
+            _ptr(h), _ptr(weight), int(taps), _ptr(state), state.stride(0) if state is not None else 0,
+            _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(batch.q_start), _ptr(batch.kv_len),
+            _ptr(batch.slots), _ptr(out), _flag(out.dtype), h.shape[0], h.shape[1], self._stream()),
+            "stream_conv")
+        self.launches += 1
+
+    @_timed("norm")
+    def stream_tail_store(self, h, state, batch):
+        """The rows of `h` at each sequence's last taps - 1 positions into its ring (row of
+        position p at p modulo taps - 1)."""
+        check(self.lib.mb_stream_tail_store(
+            _ptr(h), _ptr(state), state.stride(0), state.shape[1], _ptr(batch.q_start),
+            _ptr(batch.kv_len), _ptr(batch.slots), batch.num_seqs, h.shape[1], self._stream()),
+            "stream_tail_store")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ sigmoid attention
+
+    @_timed("rotary + store")
+    def qk_norm_rope_store(self, pre, layout, q_norm, k_norm, eps, tables, pairing, batch, cache, q,
+                           values_from_keys):
+        """pre = [q | k (| v)] float32: per-head RMS norms of q and k (weights float32, or None),
+        the rotation of their first numbers, q into `q`, keys and values into the pages; with
+        `values_from_keys` the values are the keys as projected."""
+        heads, kv_heads, dim, vdim = layout
+        self._check_limits(cache, tables)
+        cos, sin = tables if tables is not None else (None, None)
+        rot = 2 * cos.shape[1] if cos is not None else 0
+        if q.dtype != cache.k.dtype:
+            raise KernelError("qk_norm_rope_store: pages and activations differ in dtype")
+        check(self.lib.mb_qk_norm_rope_store(
+            _ptr(pre), pre.shape[1], _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), rot,
+            int(pairing == "interleaved"), _ptr(batch.positions), _ptr(batch.seq_of_token),
+            _ptr(cache.table), cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(q), heads,
+            kv_heads, dim, vdim, int(bool(values_from_keys)), cache.page_size, pre.shape[0],
+            _flag(q.dtype), self._stream()), "qk_norm_rope_store")
+        self.launches += 1
+
+    @_timed("attention")
+    def sigmoid_attention(self, q, layout, batch, cache, scale, window, keep_first, head_bias, out):
+        """out_h = sum over the seen keys of sigmoid(q_h . k * scale + head_bias[h]) v; key j is
+        seen from position p iff j <= p and (p - j < window or j < keep_first) (window 0: all)."""
+        heads, kv_heads, dim, vdim = layout
+        if vdim != dim:
+            raise KernelError("sigmoid_attention: values of another size than the keys are not built")
+        self._check_limits(cache)
+        tokens = q.shape[0]
+        group = heads // kv_heads
+        # the keys a row looks at are bounded by the window; divide them when the batch alone
+        # cannot fill the device
+        if getattr(batch, "attention_splits", None):
+            splits = batch.attention_splits
+        else:
+            reach = batch.max_kv_len if not window else min(batch.max_kv_len,
+                                                           window + keep_first + batch.max_q_len)
+            tiles = -(-batch.max_q_len * group // 16)
+            blocks = batch.num_seqs * tiles * kv_heads
+            key_tiles = -(-reach // 32)
+            splits = 1
+            if blocks < self.sm_count and key_tiles >= 4:
+                splits = max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
+        floats = self.lib.mb_sigmoid_attention_scratch_floats(tokens, heads, dim, splits)
+        scratch = self._scratch_for(floats) if floats else None
+        check(self.lib.mb_sigmoid_attention(
+            _ptr(q), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), cache.table.shape[1],
+            _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token), _ptr(head_bias),
+            _ptr(out), _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens,
+            batch.num_seqs, batch.max_q_len, heads, kv_heads, dim, cache.page_size, float(scale),
+            int(window), int(keep_first), splits, _flag(q.dtype), self._stream()),
+            "sigmoid_attention")
+        self.launches += 1 if splits == 1 else 2
 
     # ------------------------------------------------------------------ latent attention
 
@@ -748,6 +881,44 @@ class CudaOps:
             _ptr(batch.positions), _ptr(batch.seq_of_token), _ptr(cache.table), cache.table.shape[1],
             _ptr(cache.k), int(rank), cache.page_size, pre.shape[0], _flag(cache.k.dtype),
             self._stream()), "latent_norm_store")
+        self.launches += 1
+
+    @_timed("rotary + store")
+    def latent_prepare(self, pre, q_rank, q_norm, narrow, kv_offset, rank, down_norm, rot_dim, tables,
+                       pairing, eps, batch, cache):
+        """narrow = rmsnorm(pre[:, :q_rank]) * q_norm (if q_rank); with a cache, the row [c | rotated
+        part] of every token into its page: c = rmsnorm(pre[:, kv_offset : kv_offset + rank]) *
+        down_norm, the part pre[:, kv_offset + rank : + rot_dim] rotated by the token's position."""
+        if cache is not None:
+            self._check_limits(cache, tables)
+        cos, sin = tables if tables is not None else (None, None)
+        weights = [w for w in (q_norm, down_norm) if w is not None]
+        if len({w.dtype for w in weights}) > 1:
+            raise KernelError("latent_prepare: the two norm weights differ in dtype")
+        kind = narrow if narrow is not None else (cache.k if cache is not None else None)
+        if kind is None:
+            return
+        if narrow is not None and cache is not None and narrow.dtype != cache.k.dtype:
+            raise KernelError("latent_prepare: pages and activations differ in dtype")
+        check(self.lib.mb_latent_prepare(
+            _ptr(pre), pre.shape[1], int(q_rank), _ptr(q_norm), _ptr(narrow), int(kv_offset), int(rank),
+            _ptr(down_norm), _flag(weights[0].dtype) if weights else 0, int(rot_dim), _ptr(cos),
+            _ptr(sin), int(pairing == "interleaved"), float(eps), _ptr(batch.positions),
+            _ptr(batch.seq_of_token), _ptr(cache.table) if cache is not None else None,
+            cache.table.shape[1] if cache is not None else 0,
+            _ptr(cache.k) if cache is not None else None,
+            cache.page_size if cache is not None else 1, pre.shape[0], _flag(kind.dtype),
+            self._stream()), "latent_prepare")
+        self.launches += 1
+
+    @_timed("rotary + store")
+    def rope_rows(self, q, heads, row, offset, rot_dim, tables, pairing, batch):
+        """In place: q[t, h * row + offset : + rot_dim] rotated by the token's position."""
+        cos, sin = tables
+        check(self.lib.mb_rope_rows(
+            _ptr(q), _flag(q.dtype), int(heads), int(row), int(offset), int(rot_dim), _ptr(cos),
+            _ptr(sin), int(pairing == "interleaved"), _ptr(batch.positions),
+            _ptr(batch.seq_of_token), q.shape[0], self._stream()), "rope_rows")
         self.launches += 1
 
     @_timed("head product")
