@@ -776,6 +776,117 @@ def kinelix_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
     }
 
 
+SISAVIK_SIZES = {
+    # width, heads, unrotated and rotated query/key size, value size, key latent, query latent,
+    # feed-forward, key/value heads of the sigmoid attention, window, kept first tokens
+    "0.5b": (896, 14, 64, 32, 64, 96, 448, 4864, 2, 1024, 64),
+    "1.5b": (1536, 12, 128, 32, 128, 96, 768, 8960, 2, 1024, 64),
+}
+
+
+def sisavik_config(size: str) -> dict:
+    """A Sisavik model at the layer sizes of `size`: attention over a cached latent (a row of
+    128 numbers with its rotated part, as Kinelix's latent has) with a query latent and a
+    window, sigmoid attention beside a generalized delta rule, and two attention layers
+    that read the first one's rows, twice over; every layer with a dense feed-forward."""
+    width, heads, dim, rot, vdim, rank, q_rank, ff, kv_heads, window, keep = SISAVIK_SIZES[size]
+
+    def latent(source=None):
+        mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank,
+                 "q_rank": q_rank, "scale": (dim + rot) ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 10000.0, "dims": rot}}
+        if source is not None:
+            mixer["kv_from"] = source
+        return mixer
+
+    parallel = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                         "scale": dim ** -0.5, "mask": {"size": window, "keep_first": keep},
+                         "rot": {"base": 10000.0, "dims": dim}},
+                "right": {"heads": width // dim, "dim": dim, "decay_rank": 64},
+                "left_scale": 0.5, "right_scale": 0.5}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = []
+    for base in range(0, DESIGN_LAYERS, 4):
+        layers += [{"type": "latent_attention", "mixer": latent(), "mlp": mlp},
+                   {"type": "parallel", "mixer": parallel, "mlp": mlp},
+                   {"type": "latent_attention", "mixer": latent(base), "mlp": mlp},
+                   {"type": "latent_attention", "mixer": latent(base), "mlp": mlp}]
+    return {"architecture": "Sisavik", "width": width, "vocab": DESIGN_VOCAB,
+            "max_positions": MODEL_LEN, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "layers": layers[:DESIGN_LAYERS]}
+
+
+def seen_pairs(tokens: int, before: int, window: int, keep: int = 0) -> int:
+    """How many (query, key) pairs a portion of `tokens` behind `before` cached tokens has
+    under a window with kept first tokens."""
+    total = 0
+    for p in range(before, before + tokens):
+        total += p + 1 if not window or p < window else window + min(keep, p + 1 - window)
+    return total
+
+
+def sisavik_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
+    """Per class of kernel call, what a Sisavik model has to read (decode step, bytes) or
+    compute (prompt step, flops; bytes for the classes that only move data)."""
+    w, v = raw["width"], raw["vocab"]
+    taps = raw["canon"]["taps"]
+    products = head = 2 * v * w
+    gated = head_products = att_bytes = att_flops = state_bytes = scan_flops = rec_tokens = 0
+    rotary = 0
+    norms = 1
+    for layer in raw["layers"]:
+        m = layer["mixer"]
+        norms += 2                                   # the input convolution and the norm behind
+        if layer["type"] == "latent_attention":
+            own = m.get("kv_from") is None
+            row, q_head = m["kv_rank"] + m["rot_dim"], m["dim"] + m["rot_dim"]
+            rows = m["q_rank"] + (row if own else 0)
+            products += 2 * (rows * w + m["heads"] * q_head * m["q_rank"] + m["heads"] * m["vdim"] * w)
+            head_products += 2 * m["heads"] * row * (q_head + m["vdim"])
+            reach = min(context + 1, m["mask"]["size"] or context + 1)
+            att_bytes += batch * reach * 2 * row
+            att_flops += m["heads"] * 4 * row * seen_pairs(tokens, 0, m["mask"]["size"])
+            rotary += 4 * rows + 2 * (m["q_rank"] + (row if own else 0)) + 4 * m["heads"] * row
+        else:
+            left, right = m["left"], m["right"]
+            qk = (left["heads"] + left["kv_heads"]) * left["dim"]
+            products += 2 * (qk * w + left["heads"] * left["dim"] * w)
+            mask = left["mask"]
+            reach = min(context + 1, (mask["size"] + mask["keep_first"]) if mask["size"] else context + 1)
+            att_bytes += batch * reach * 2 * 2 * left["kv_heads"] * left["dim"]
+            att_flops += left["heads"] * 4 * left["dim"] * seen_pairs(tokens, 0, mask["size"],
+                                                                      mask["keep_first"])
+            rotary += 4 * qk + 2 * (left["heads"] + 2 * left["kv_heads"]) * left["dim"]
+            keys = right["heads"] * right["dim"]
+            proj = 5 * keys + right["decay_rank"]
+            products += 2 * (proj * w + keys * right["decay_rank"] + keys * w)
+            state_bytes += 2 * 4 * right["heads"] * right["dim"] * right["dim"]
+            scan_flops += 10 * right["heads"] * right["dim"] * right["dim"]
+            rec_tokens += 4 * (5 * keys + 2 * right["decay_rank"] + 2 * keys) + 2 * keys
+        if layer["mlp"] is not None:
+            norms += 2
+            gated += 2 * 2 * layer["mlp"]["ff"] * w
+            products += 2 * layer["mlp"]["ff"] * w
+    t = tokens
+    # a convolution reads the float32 stream and writes activations; a norm reads the float32
+    # stream and the sublayer's output and writes the stream
+    per_row = w * (4 + 2 + 4 + 2 + 4) // 2
+    return {
+        "decode": {"product": ("hbm", products), "gated product": ("hbm", gated),
+                   "attention": ("hbm", att_bytes), "head product": ("hbm", head_products),
+                   "recurrence": ("hbm", batch * (state_bytes + rec_tokens)),
+                   "rotary + store": ("hbm", batch * rotary),
+                   "norm": ("hbm", norms * batch * per_row)},
+        "prefill": {"product": ("tensor", t * (products - head) + head),
+                    "gated product": ("tensor", t * gated),
+                    "attention": ("tensor", att_flops),
+                    "head product": ("tensor", t * head_products),
+                    "recurrence": ("tensor", t * scan_flops),
+                    "rotary + store": ("hbm", t * rotary),
+                    "norm": ("hbm", norms * t * per_row)},
+    }
+
+
 def classes_of(torch, runner, batch, context, vocab, costs, peak) -> dict:
     """Milliseconds per class of kernel call of a decode step and of a prompt step (events
     around every call, the launches queued behind a delay on the device), with the fraction
@@ -837,7 +948,10 @@ def run_designs(args) -> dict:
         fegenex, qwen2 = design_configs(size)
         # the design asked for, beside the closest models this engine has at the same sizes
         models = ((("fegenex", fegenex), ("qwen2", qwen2)) if args.design == "fegenex" else
-                  (("kinelix", kinelix_config(size)), ("fegenex", fegenex), ("qwen2", qwen2)))
+                  (("kinelix", kinelix_config(size)), ("fegenex", fegenex), ("qwen2", qwen2))
+                  if args.design == "kinelix" else
+                  (("sisavik", sisavik_config(size)), ("kinelix", kinelix_config(size)),
+                   ("qwen2", qwen2)))
         for label, raw in models:
             _entry, config = config_from_dict(raw)
             tensors = random_tensors(config, SEED, torch.bfloat16)
@@ -850,6 +964,7 @@ def run_designs(args) -> dict:
                                                 max(3, args.warmup))
             costs = (design_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "fegenex"
                      else kinelix_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "kinelix"
+                     else sisavik_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "sisavik"
                      else class_costs(raw, batch, CONTEXT, PREFILL_TOKENS))
             row[label] = {"prefill_ms": round(prefill_ms, 3),
                           "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1),
@@ -998,7 +1113,7 @@ def main() -> int:
                    help="run one part only (for profilers and side workloads); prints its own JSON")
     p.add_argument("--size", default=None, choices=tuple(SIZES),
                    help="layer sizes of --only decode/prefill/mixed (default 0.5b; mixed: 1.5b)")
-    p.add_argument("--design", default="fegenex", choices=("fegenex", "kinelix"),
+    p.add_argument("--design", default="fegenex", choices=("fegenex", "kinelix", "sisavik"),
                    help="which design --only designs measures beside the closest existing models")
     p.add_argument("--policy", default="lpm", choices=("fcfs", "lpm", "lpm_aging"))
     p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")

@@ -14,53 +14,11 @@
 // sum, and the output accumulate in float32; probabilities are rounded to bfloat16 for the
 // P.V product (the usual flash-attention arrangement).
 #include "tcgen05.cuh"
+#include "mma_sync.cuh"
 
 namespace mb {
 
 constexpr int MMA_BN = 64;  // keys per tile
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-        "{%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
-    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
-    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zeroed
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(gmem),
-                 "r"(bytes));
-}
-
-// 2^x by the special-function unit (ex2.approx: relative error about 2^-22, far below the
-// bfloat16 rounding that follows); 2^-inf = 0.
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 template <int D, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)

@@ -17,6 +17,7 @@
 // gridDim.z and the partial sums are added in a fixed order by a second kernel. Scores,
 // sigmoids and sums are float32.
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace mb {
 
@@ -280,6 +281,243 @@ int launch_sigmoid(const void* q, const void* k_pages, const void* v_pages, cons
     return launch_status();
 }
 
+// ---- prompt portions in bfloat16 on the tensor cores ------------------------------------------
+// The same sum for head sizes 64 and 128 with mma.sync m16n8k16: a block of NWARPS warps takes
+// NWARPS * 16 rows (a warp 16 of them, a thread rows g and g + 8 of those), keys are walked in
+// tiles of 64 that cp.async brings into two stages (16-byte pieces, XOR-swizzled by the row),
+// S = Q K^T accumulates in float32, the sigmoid of every seen score is taken in float32 and
+// rounded to bfloat16 as the A operand of O += P V (values read transposed by ldmatrix). There
+// is no running maximum, no rescaling and no denominator. Tiles: those of the kept first
+// tokens, then those of the rows' windows, no tile twice.
+constexpr int SGM_BN = 64;
+
+template <int D, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                             const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ table,
+                             int max_pages, const int* __restrict__ q_start,
+                             const int* __restrict__ kv_len_of, const float* __restrict__ head_bias,
+                             __nv_bfloat16* __restrict__ out, float* __restrict__ part, int n_q, int n_kv,
+                             int page_size, float scale, int window, int keep_first, int tiles_per_seq,
+                             int num_splits) {
+    grid_dependency_sync();
+    constexpr int ROWS = NWARPS * 16;
+    constexpr int CH = D / 8;        // 16-byte pieces per row
+    constexpr int THREADS = NWARPS * 32;
+    extern __shared__ __align__(128) unsigned char sgm_raw[];
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(sgm_raw);   // [ROWS][D]
+    __nv_bfloat16* k_s = q_s + ROWS * D;                              // [2][SGM_BN][D]
+    __nv_bfloat16* v_s = k_s + 2 * SGM_BN * D;                        // [2][SGM_BN][D]
+
+    const int seq = blockIdx.x / tiles_per_seq;
+    const int tile = tiles_per_seq - 1 - (blockIdx.x - seq * tiles_per_seq);
+    const int kvh = blockIdx.y, split = blockIdx.z;
+    const int group = n_q / n_kv;
+    const int q_begin = q_start[seq];
+    const int q_len = q_start[seq + 1] - q_begin;
+    const int row0 = tile * ROWS;
+    if (row0 >= q_len * group) return;
+    const int kv_len = kv_len_of[seq];
+    const int first_pos = kv_len - q_len;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int idx = tid; idx < ROWS * CH; idx += THREADS) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int row = row0 + r;
+        const int tok = row / group, hg = row - tok * group;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (tok < q_len)
+            val = *reinterpret_cast<const uint4*>(q + ((int64_t)(q_begin + tok) * n_q + kvh * group + hg) * D +
+                                                  c * 8);
+        *reinterpret_cast<uint4*>(q_s + r * D + ((c ^ (r & 7)) * 8)) = val;
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(qf[ks], q_s + r * D + ((c ^ (r & 7)) * 8));
+    }
+
+    const int g = lane >> 2, t4 = lane & 3;
+    int pos[2];
+    bool row_ok[2];
+    float bias2[2];                       // the head's number in units of log2(e)
+    constexpr float LOG2E = 1.4426950408889634f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = row0 + warp * 16 + g + h * 8;
+        const int tok = row / group, hg = row - tok * group;
+        row_ok[h] = tok < q_len;
+        pos[h] = first_pos + tok;
+        bias2[h] = head_bias[kvh * group + hg] * LOG2E;
+    }
+    const int wrow0 = row0 + warp * 16;
+    const bool warp_rows_ok = (wrow0 + 15) / group < q_len;
+    const int warp_pos_min = first_pos + wrow0 / group;
+    const int warp_pos_max = first_pos + (wrow0 + 15) / group;
+
+    // the key tiles of this block: [0, head_hi) for the kept first tokens, [t_lo, t_hi) for the
+    // windows; walked as one list with the overlap dropped
+    const int tok_min = row0 / group;
+    int tok_max = (row0 + ROWS - 1) / group;
+    if (tok_max > q_len - 1) tok_max = q_len - 1;
+    const int p_min = first_pos + tok_min, p_max = first_pos + tok_max;
+    const int t_hi = p_max / SGM_BN + 1;
+    int t_lo = 0;
+    if (window > 0 && p_min - window + 1 > 0) t_lo = (p_min - window + 1) / SGM_BN;
+    int head_hi = 0;
+    if (window > 0 && keep_first > 0) head_hi = (keep_first + SGM_BN - 1) / SGM_BN;
+    if (head_hi > t_lo) head_hi = t_lo;
+    const int count = head_hi + (t_hi - t_lo);
+    int n_lo = 0, n_hi = count;
+    if (num_splits > 1) {
+        const int per = (count + num_splits - 1) / num_splits;
+        n_lo = split * per;
+        n_hi = n_lo + per < count ? n_lo + per : count;
+    }
+    auto tile_of = [&](int n) { return n < head_hi ? n : t_lo + (n - head_hi); };
+
+    auto load_tile = [&](int stage, int kt) {
+        __nv_bfloat16* kd = k_s + stage * SGM_BN * D;
+        __nv_bfloat16* vd = v_s + stage * SGM_BN * D;
+        for (int idx = tid; idx < SGM_BN * CH; idx += THREADS) {
+            const int j = idx / CH, c = idx - j * CH;
+            const int key = kt * SGM_BN + j;
+            int page = -1;
+            if (key < kv_len) page = table_page(table, seq, max_pages, key / page_size);
+            const bool valid = page >= 0;
+            const int64_t at =
+                valid ? (((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * D + c * 8 : 0;
+            const int sw = (c ^ (j & 7)) * 8;
+            cp_async_16(kd + j * D + sw, k_pages + at, valid);
+            cp_async_16(vd + j * D + sw, v_pages + at, valid);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const float scale2 = scale * LOG2E;
+
+    if (n_lo < n_hi) load_tile(0, tile_of(n_lo));
+    for (int n = n_lo; n < n_hi; ++n) {
+        const int kt = tile_of(n);
+        const int stage = (n - n_lo) & 1;
+        if (n + 1 < n_hi) {
+            load_tile(stage ^ 1, tile_of(n + 1));
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        const __nv_bfloat16* kt_s = k_s + stage * SGM_BN * D;
+        const __nv_bfloat16* vt_s = v_s + stage * SGM_BN * D;
+
+        float s[SGM_BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < SGM_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < SGM_BN / 16; ++n2) {
+                uint32_t b[4];
+                const int j = n2 * 16 + (lane & 7) + (lane >> 4) * 8;
+                const int c = ks * 2 + ((lane >> 3) & 1);
+                ldmatrix_x4(b, kt_s + j * D + ((c ^ (j & 7)) * 8));
+                mma_bf16(s[2 * n2], qf[ks], b[0], b[1]);
+                mma_bf16(s[2 * n2 + 1], qf[ks], b[2], b[3]);
+            }
+        }
+
+        // sigmoid(x) = 1 / (1 + 2^(-x log2 e)), float32; an unseen key weighs nothing. A tile
+        // that every row of the warp sees whole needs no test per element.
+        const int tile_first = kt * SGM_BN, tile_last = tile_first + SGM_BN - 1;
+        const bool whole = warp_rows_ok && tile_last <= warp_pos_min && tile_last < kv_len &&
+                           (window <= 0 || tile_first > warp_pos_max - window || tile_last < keep_first);
+#pragma unroll
+        for (int nt = 0; nt < SGM_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                bool seen = true;
+                if (!whole) {
+                    const int key = tile_first + nt * 8 + 2 * t4 + (e & 1);
+                    seen = row_ok[h] && key <= pos[h] && key < kv_len;
+                    if (window > 0) seen = seen && (key > pos[h] - window || key < keep_first);
+                }
+                const float x2 = fmaf(s[nt][e], scale2, bias2[h]);
+                s[nt][e] = seen ? __fdividef(1.f, 1.f + fast_exp2(-x2)) : 0.f;
+            }
+        }
+
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < SGM_BN / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int d2 = 0; d2 < D / 16; ++d2) {
+                uint32_t b[4];
+                const int j = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int c = d2 * 2 + (lane >> 4);
+                ldmatrix_x4_trans(b, vt_s + j * D + ((c ^ (j & 7)) * 8));
+                mma_bf16(o[2 * d2], a, b[0], b[1]);
+                mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();  // everyone is done with this stage before it is refilled
+    }
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!row_ok[h]) continue;
+        const int row = row0 + warp * 16 + g + h * 8;
+        const int tok = row / group, hg = row - tok * group;
+        const int64_t flat = (int64_t)(q_begin + tok) * n_q + kvh * group + hg;
+        if (num_splits == 1) {
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(o[i][2 * h], o[i][2 * h + 1]);
+                *reinterpret_cast<__nv_bfloat162*>(out + flat * D + i * 8 + 2 * t4) = v;
+            }
+        } else {
+            const int64_t at = flat * num_splits + split;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i)
+                *reinterpret_cast<float2*>(part + at * D + i * 8 + 2 * t4) =
+                    make_float2(o[i][2 * h], o[i][2 * h + 1]);
+        }
+    }
+}
+
+template <int D, int NWARPS>
+int launch_sigmoid_mma(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                       int max_pages, const int* q_start, const int* kv_len, const float* head_bias,
+                       void* out, float* part, int n_q, int n_kv, int page_size, float scale, int window,
+                       int keep_first, int num_seqs, int tiles_per_seq, int num_splits, cudaStream_t s) {
+    typedef __nv_bfloat16 bf;
+    const size_t smem = (size_t)(NWARPS * 16 + 4 * SGM_BN) * D * sizeof(bf);
+    static bool raised = false;
+    if (smem > 40 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(sigmoid_attention_mma_kernel<D, NWARPS>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return MB_ERR_UNSUPPORTED_SIZE;
+        raised = true;
+    }
+    dim3 grid(num_seqs * tiles_per_seq, n_kv, num_splits);
+    MB_LAUNCH((sigmoid_attention_mma_kernel<D, NWARPS>), grid, NWARPS * 32, smem, s, (const bf*)q,
+              (const bf*)k_pages, (const bf*)v_pages, table, max_pages, q_start, kv_len, head_bias,
+              (bf*)out, part, n_q, n_kv, page_size, scale, window, keep_first, tiles_per_seq,
+              num_splits);
+    return launch_status();
+}
+
 template <typename T>
 int dispatch_sigmoid(int nc, const void* q, const void* k_pages, const void* v_pages,
                      const int* table, int max_pages, const int* q_start, const int* kv_len,
@@ -387,5 +625,42 @@ MB_EXPORT int mb_sigmoid_attention(const void* q, const void* k_pages, const voi
     else
         MB_LAUNCH((sigmoid_attention_sum_kernel<__nv_bfloat16>), grid, 64, 0, s, scratch, seq_of_token,
                   (__nv_bfloat16*)out, n_q, d, num_splits);
+    return launch_status();
+}
+
+MB_EXPORT int mb_sigmoid_attention_mma_supports(int d) { return d == 64 || d == 128; }
+
+// The tensor-core kernel: bfloat16, head sizes 64 and 128; everything else as above. A row
+// tile is 64 rows (four warps).
+MB_EXPORT int mb_sigmoid_attention_mma(const void* q, const void* k_pages, const void* v_pages,
+                                       const int* table, int max_pages, const int* q_start,
+                                       const int* kv_len, const int* seq_of_token,
+                                       const float* head_bias, void* out, float* scratch,
+                                       long long scratch_floats, int tokens, int num_seqs,
+                                       int max_q_len, int n_q, int n_kv, int d, int page_size,
+                                       float scale, int window, int keep_first, int num_splits,
+                                       void* stream) {
+    if (tokens <= 0 || num_seqs <= 0 || max_q_len <= 0) return MB_OK;
+    if (!mb_sigmoid_attention_mma_supports(d) || n_kv <= 0 || n_q % n_kv) return MB_ERR_UNSUPPORTED_SIZE;
+    if (page_size <= 0 || window < 0 || keep_first < 0) return MB_ERR_UNSUPPORTED_SIZE;
+    if (num_splits < 1) num_splits = 1;
+    if (n_kv > 65535 || num_splits > 65535 || n_q > 65535) return MB_ERR_UNSUPPORTED_SIZE;
+    if (num_splits > 1 &&
+        (!scratch || scratch_floats < mb_sigmoid_attention_scratch_floats(tokens, n_q, d, num_splits)))
+        return MB_ERR_SCRATCH;
+    const int group = n_q / n_kv;
+    const int tiles_per_seq = (max_q_len * group + 63) / 64;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int rc = d == 64
+        ? launch_sigmoid_mma<64, 4>(q, k_pages, v_pages, table, max_pages, q_start, kv_len, head_bias, out,
+                                    scratch, n_q, n_kv, page_size, scale, window, keep_first, num_seqs,
+                                    tiles_per_seq, num_splits, s)
+        : launch_sigmoid_mma<128, 4>(q, k_pages, v_pages, table, max_pages, q_start, kv_len, head_bias, out,
+                                     scratch, n_q, n_kv, page_size, scale, window, keep_first, num_seqs,
+                                     tiles_per_seq, num_splits, s);
+    if (rc != MB_OK || num_splits == 1) return rc;
+    dim3 grid(tokens, n_q);
+    MB_LAUNCH((sigmoid_attention_sum_kernel<__nv_bfloat16>), grid, 64, 0, s, scratch, seq_of_token,
+              (__nv_bfloat16*)out, n_q, d, num_splits);
     return launch_status();
 }

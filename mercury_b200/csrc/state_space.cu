@@ -620,8 +620,8 @@ delta_rule_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ 
 // v_p and o_p = y - x ((a * u) . r) + v_p (k . r): one pass over the column per token. S is
 // [dim][vdim] at cells[slot][(head * dim + d) * vdim + p]. The split of a head over lanes is the
 // one described at the top of this file (eight lanes a column, four neighbouring rows at a
-// time). The decay is computed in double and rounded once.
-template <int DPT, typename S>
+// time). With the matrices in double the decay is computed in double and rounded once.
+template <int DPT, typename S, int TILE>
 __global__ void __launch_bounds__(512)
 general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int at_k, int at_v, int at_a,
                           const float* __restrict__ decay_in, float decay_scale, float unit_eps,
@@ -633,13 +633,11 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
     constexpr int SL = SS_SLICES;
     constexpr int DP = DPT * SL;
     const int cols = (blockDim.x >> 5) * (32 / SL);
-    float* wr_s = sm;                          // r, then w * r    [SS_TILE][DP]
-    float* k_s = wr_s + SS_TILE * DP;          // k
-    float* au_s = k_s + SS_TILE * DP;          // raw a, then a * u
-    float* w_s = au_s + SS_TILE * DP;          // raw decay, then w
-    float* u_s = w_s + SS_TILE * DP;           // u
-    float* v_s = u_s + SS_TILE * DP;           // [SS_TILE][cols]
-    __shared__ float aur_s[SS_TILE], kr_s[SS_TILE];
+    // two stages of [r, then w * r | k | raw a, then a * u | raw decay, then w | v], filled by
+    // cp.async a tile ahead, and the unit keys of the tile being walked
+    const int stage_floats = 4 * TILE * DP + TILE * cols;
+    float* u_s = sm + 2 * stage_floats;        // [TILE][DP]
+    __shared__ float aur_s[TILE], kr_s[TILE];
     const int head = blockIdx.x / chunks_per_head, chunk = blockIdx.x - head * chunks_per_head;
     const int seq = blockIdx.y;
     const int begin = q_start[seq], end = q_start[seq + 1];
@@ -656,20 +654,44 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
         const int d = row_in<SL>(slice, i);
         s[i] = (live && d < dim) ? (S)mine[(int64_t)d * vdim + p] : (S)0;
     }
-    for (int t0 = begin; t0 < end; t0 += SS_TILE) {
-        const int nt = min(SS_TILE, end - t0);
+    auto fetch = [&](int stage, int t0) {
+        float* r_to = sm + stage * stage_floats;
+        float* k_to = r_to + TILE * DP;
+        float* a_to = k_to + TILE * DP;
+        float* w_to = a_to + TILE * DP;
+        float* v_to = w_to + TILE * DP;
+        const int nt = min(TILE, end - t0);
         for (int idx = tid; idx < nt * DP; idx += blockDim.x) {
             const int tt = idx / DP, d = idx - tt * DP;
             const bool take = d < dim;
             const float* row = pre + (int64_t)(t0 + tt) * ld + head * dim + d;
-            wr_s[idx] = take ? row[at_r] : 0.f;
-            k_s[idx] = take ? row[at_k] : 0.f;
-            au_s[idx] = take ? row[at_a] : 0.f;
-            w_s[idx] = take ? decay_in[(int64_t)(t0 + tt) * heads * dim + head * dim + d] : 0.f;
+            stage_float(r_to + idx, take ? row + at_r : pre, take);
+            stage_float(k_to + idx, take ? row + at_k : pre, take);
+            stage_float(a_to + idx, take ? row + at_a : pre, take);
+            stage_float(w_to + idx, take ? decay_in + (int64_t)(t0 + tt) * heads * dim + head * dim + d : pre,
+                        take);
         }
         for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
             const int tt = idx / cols, pp = chunk * cols + (idx - tt * cols);
-            v_s[idx] = pp < vdim ? pre[(int64_t)(t0 + tt) * ld + at_v + head * vdim + pp] : 0.f;
+            const bool take = pp < vdim;
+            stage_float(v_to + idx, take ? pre + (int64_t)(t0 + tt) * ld + at_v + head * vdim + pp : pre, take);
+        }
+        stage_commit();
+    };
+    fetch(0, begin);
+    int turn = 0;
+    for (int t0 = begin; t0 < end; t0 += TILE, turn ^= 1) {
+        const int nt = min(TILE, end - t0);
+        float* wr_s = sm + turn * stage_floats;    // r, then w * r    [TILE][DP]
+        float* k_s = wr_s + TILE * DP;             // k
+        float* au_s = k_s + TILE * DP;             // raw a, then a * u
+        float* w_s = au_s + TILE * DP;             // raw decay, then w
+        const float* v_s = w_s + TILE * DP;        // [TILE][cols]
+        if (t0 + TILE < end) {
+            fetch(turn ^ 1, t0 + TILE);
+            stage_wait_but_one();
+        } else {
+            stage_wait_all();
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += warps) {
@@ -683,7 +705,14 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
                 const float r = wr_s[at], k = k_s[at];
                 const float u = k * rk;
                 const float a = 1.f / (1.f + expf(-au_s[at]));
-                const float w = (float)exp(-(double)decay_scale / (1.0 + exp(-(double)w_s[at])));
+                // held in double, the matrices are owed a decay rounded once; beside bfloat16
+                // activations float arithmetic serves (a dependent chain of double-precision
+                // exponentials per tile was most of this kernel's time)
+                float w;
+                if constexpr (sizeof(S) == 8)
+                    w = (float)exp(-(double)decay_scale / (1.0 + exp(-(double)w_s[at])));
+                else
+                    w = expf(-decay_scale / (1.f + expf(-w_s[at])));
                 u_s[at] = u;
                 au_s[at] = a * u;
                 w_s[at] = w;
@@ -697,7 +726,7 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
                 aur_s[tt] = aur;
                 kr_s[tt] = kr;
             }
-            // rows beyond dim stay as staged: zero everywhere, so padded rows of S stay zero
+            // rows beyond dim were staged as zeros and stay so, so padded rows of S stay zero
             for (int d = dim + lane; d < DP; d += 32) u_s[tt * DP + d] = 0.f;
         }
         __syncthreads();
@@ -735,7 +764,7 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
                 out[(int64_t)(t0 + tt) * inner + head * vdim + p] =
                     (float)(y - x * (S)aur_s[tt] + vp * (S)kr_s[tt]);
         }
-        __syncthreads();                      // the tile may be refilled
+        __syncthreads();                      // the stage may be refilled, the unit keys rewritten
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -929,7 +958,8 @@ static void scan_shape(int vdim, int heads, int num_seqs, int* warps, int* chunk
 // matrices only: 256 rows).
 template <typename K>
 static bool allow_smem(K kernel, size_t smem) {
-    return smem <= 48 * 1024 ||
+    // a kernel's static arrays count toward the 48 KB that need no opt-in: leave them room
+    return smem + 2048 <= 48 * 1024 ||
            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
 }
 
@@ -1072,29 +1102,34 @@ MB_EXPORT int mb_general_delta_scan(const float* pre, int ld, int at_r, int at_k
     int warps = (vdim + 3) / 4;
     if (warps < 4) warps = 4;
     if (warps > 16) warps = 16;
+    // a step of few sequences: narrower blocks over more of the device (a column's walk is
+    // the same whichever block holds it, so the result does not depend on the split)
+    while (warps > 8 && (long long)heads * num_seqs * ((vdim + warps * 4 - 1) / (warps * 4)) < 148)
+        warps /= 2;
     const int cols = warps * 4;
     const int chunks = (vdim + cols - 1) / cols;
     dim3 grid(heads * chunks, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-#define MB_GD_CASE(DPT)                                                                            \
+#define MB_GD_CASE(DPT, TILE)                                                                      \
     do {                                                                                           \
-        const size_t smem = (size_t)(5 * SS_TILE * DPT * SS_SLICES + SS_TILE * cols) * sizeof(float); \
-        if (!allow_smem(general_delta_scan_kernel<DPT, double>, smem) ||                           \
-            !allow_smem(general_delta_scan_kernel<DPT, float>, smem))                              \
+        const size_t smem = (size_t)(9 * TILE * DPT * SS_SLICES + 2 * TILE * cols) * sizeof(float); \
+        if (!allow_smem(general_delta_scan_kernel<DPT, double, TILE>, smem) ||                     \
+            !allow_smem(general_delta_scan_kernel<DPT, float, TILE>, smem))                        \
             return MB_ERR_UNSUPPORTED_SIZE;                                                        \
         if (precise)                                                                               \
-            MB_LAUNCH((general_delta_scan_kernel<DPT, double>), grid, warps * 32, smem, s, pre, ld, \
-                      at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,              \
+            MB_LAUNCH((general_delta_scan_kernel<DPT, double, TILE>), grid, warps * 32, smem, s, pre, \
+                      ld, at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,          \
                       (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks);        \
         else                                                                                       \
-            MB_LAUNCH((general_delta_scan_kernel<DPT, float>), grid, warps * 32, smem, s, pre, ld, \
-                      at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,              \
+            MB_LAUNCH((general_delta_scan_kernel<DPT, float, TILE>), grid, warps * 32, smem, s, pre, \
+                      ld, at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,          \
                       (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks);        \
     } while (0)
-    if (dim <= 32) MB_GD_CASE(4);
-    else if (dim <= 64) MB_GD_CASE(8);
-    else if (dim <= 128) MB_GD_CASE(16);
-    else MB_GD_CASE(32);
+    // (the widest matrices stage 16 tokens at a time: two stages of 32 would not fit)
+    if (dim <= 32) MB_GD_CASE(4, 32);
+    else if (dim <= 64) MB_GD_CASE(8, 32);
+    else if (dim <= 128) MB_GD_CASE(16, 32);
+    else MB_GD_CASE(32, 16);
 #undef MB_GD_CASE
     return launch_status();
 }

@@ -191,7 +191,7 @@ MB_EXPORT int mb_scaled_add_norm(float* h, const void* delta, int delta_dtype, c
 #define MB_SAN_CASE(TD, TO)                                                                       \
     do {                                                                                          \
         static size_t raised = 0;                                                                 \
-        if (smem > 48 * 1024 && smem > raised) {                                                  \
+        if (smem + 256 > 48 * 1024 && smem > raised) {                                                \
             if (cudaFuncSetAttribute(scaled_add_norm_kernel<TD, TO>,                              \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=   \
                 cudaSuccess)                                                                      \
@@ -232,7 +232,7 @@ MB_EXPORT int mb_rmsnorm_add_pair(float* h, const void* delta, const void* delta
 #define MB_RAP_CASE(TD)                                                                           \
     do {                                                                                          \
         static size_t raised = 0;                                                                 \
-        if (smem > 48 * 1024 && smem > raised) {                                                  \
+        if (smem + 256 > 48 * 1024 && smem > raised) {                                                \
             if (cudaFuncSetAttribute(rmsnorm_add_pair_kernel<TD>,                                 \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=   \
                 cudaSuccess)                                                                      \

@@ -161,6 +161,9 @@ _SIGNATURES = {
     "mb_sigmoid_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_sigmoid_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "mb_general_delta_scan": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float,
                               c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_void_p],
@@ -212,6 +215,8 @@ def load():
     lib.mb_mixed_head_scratch_floats.restype = c_longlong
     lib.mb_mamba2_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int]
     lib.mb_mamba2_scratch_floats.restype = c_longlong
+    lib.mb_sigmoid_attention_mma_supports.argtypes = [c_int]
+    lib.mb_sigmoid_attention_mma_supports.restype = c_int
     lib.mb_sigmoid_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_sigmoid_attention_scratch_floats.restype = c_longlong
     _LIB = lib

@@ -836,15 +836,24 @@ class CudaOps:
         self.launches += 1
 
     @_timed("attention")
-    def sigmoid_attention(self, q, layout, batch, cache, scale, window, keep_first, head_bias, out):
+    def sigmoid_attention(self, q, layout, batch, cache, scale, window, keep_first, head_bias, out,
+                          kernel: str | None = None):
         """out_h = sum over the seen keys of sigmoid(q_h . k * scale + head_bias[h]) v; key j is
-        seen from position p iff j <= p and (p - j < window or j < keep_first) (window 0: all)."""
+        seen from position p iff j <= p and (p - j < window or j < keep_first) (window 0: all).
+        `kernel` forces "mma" or "simt"; by default prompt portions in bfloat16 with a head size
+        of 64 or 128 run on the tensor cores, everything else on the CUDA cores."""
         heads, kv_heads, dim, vdim = layout
         if vdim != dim:
             raise KernelError("sigmoid_attention: values of another size than the keys are not built")
         self._check_limits(cache)
         tokens = q.shape[0]
         group = heads // kv_heads
+        mma_ok = q.dtype == torch.bfloat16 and bool(self.lib.mb_sigmoid_attention_mma_supports(dim))
+        if kernel == "mma" and not mma_ok:
+            raise KernelError(f"the tensor-core sigmoid attention takes bfloat16 with head size 64 or "
+                              f"128, not {q.dtype} with {dim}")
+        use_mma = mma_ok and (kernel == "mma" or (kernel is None and batch.max_q_len * group >= 64))
+        rows, keys = (64, 64) if use_mma else (16, 32)
         # the keys a row looks at are bounded by the window; divide them when the batch alone
         # cannot fill the device
         if getattr(batch, "attention_splits", None):
@@ -852,21 +861,24 @@ class CudaOps:
         else:
             reach = batch.max_kv_len if not window else min(batch.max_kv_len,
                                                            window + keep_first + batch.max_q_len)
-            tiles = -(-batch.max_q_len * group // 16)
+            tiles = -(-batch.max_q_len * group // rows)
             blocks = batch.num_seqs * tiles * kv_heads
-            key_tiles = -(-reach // 32)
+            key_tiles = -(-reach // keys)
             splits = 1
             if blocks < self.sm_count and key_tiles >= 4:
                 splits = max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
         floats = self.lib.mb_sigmoid_attention_scratch_floats(tokens, heads, dim, splits)
         scratch = self._scratch_for(floats) if floats else None
-        check(self.lib.mb_sigmoid_attention(
-            _ptr(q), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), cache.table.shape[1],
-            _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token), _ptr(head_bias),
-            _ptr(out), _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens,
-            batch.num_seqs, batch.max_q_len, heads, kv_heads, dim, cache.page_size, float(scale),
-            int(window), int(keep_first), splits, _flag(q.dtype), self._stream()),
-            "sigmoid_attention")
+        common = (_ptr(q), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), cache.table.shape[1],
+                  _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token), _ptr(head_bias),
+                  _ptr(out), _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens,
+                  batch.num_seqs, batch.max_q_len, heads, kv_heads, dim, cache.page_size, float(scale),
+                  int(window), int(keep_first), splits)
+        if use_mma:
+            check(self.lib.mb_sigmoid_attention_mma(*common, self._stream()), "sigmoid_attention (mma)")
+        else:
+            check(self.lib.mb_sigmoid_attention(*common, _flag(q.dtype), self._stream()),
+                  "sigmoid_attention")
         self.launches += 1 if splits == 1 else 2
 
     # ------------------------------------------------------------------ latent attention

@@ -144,9 +144,10 @@ def make_runner(name, ops, device, dtype, page=16, num_tokens=512, poison=True, 
     from mercury_b200.engine.runner import ModelRunner
 
     _raw, config, own = sisavik_model(name)
+    more.setdefault("max_model_len", num_tokens)     # the pool may be smaller than a request is long
     return ModelRunner(config=config, tensors=tensors if tensors is not None else own, dtype=dtype,
                        device=device, page_size=page, num_pages=num_tokens // page, max_seqs=4,
-                       max_step_tokens=num_tokens, max_model_len=num_tokens, ops=ops,
+                       max_step_tokens=num_tokens, ops=ops,
                        poison_pages=poison, **more)
 
 

@@ -138,19 +138,25 @@ SIGMOID_CASES = [
     (16, 2, 64, 16, (130, 1), (130, 2000), 0, 0),
     (5, 5, 24, 16, (1, 2), (300, 301), 1, 3),
     (2, 1, 40, 64, (1,), (1500,), 1024, 1),
+    (14, 2, 64, 16, (300, 1, 70), (300, 500, 331), 100, 70),
+    (4, 4, 128, 16, (129, 64), (400, 64), 65, 64),
+    (8, 1, 64, 32, (200,), (1000,), 128, 129),
 ]
 
 
-@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
+                                          ("mma", torch.bfloat16)], ids=["f32", "bf16", "bf16-mma"])
 @pytest.mark.parametrize("splits", [0, 1, 5])
 @pytest.mark.parametrize("case", range(len(SIGMOID_CASES)), ids=lambda i: f"case{i}")
-def test_sigmoid_attention_against_its_twin(ops, twin, dtype, splits, case):
+def test_sigmoid_attention_against_its_twin(ops, twin, kernel, dtype, splits, case):
     """`splits`: the keys of a row tile divided over that many blocks (0: the kernel's own
     choice), summed afterwards. Pages behind the window and not among the kept first tokens
     are absent from the table."""
     from test_kernels_gpu import make_batch
 
     heads, kv_heads, dim, page, q_lens, kv_lens, window, keep = SIGMOID_CASES[case]
+    if kernel == "mma" and not ops.lib.mb_sigmoid_attention_mma_supports(dim):
+        pytest.skip("head sizes left to the CUDA-core kernel")
     num_pages = sum(-(-kv // page) for kv in kv_lens) + 3
     batch, table = make_batch(q_lens, kv_lens, page, num_pages, pad_tokens=2, seed=case)
     if window:
@@ -166,7 +172,7 @@ def test_sigmoid_attention_against_its_twin(ops, twin, dtype, splits, case):
     got = torch.zeros((batch.num_tokens, heads * dim), dtype=dtype, device="cuda")
     want = torch.zeros_like(got)
     layout = (heads, kv_heads, dim, dim)
-    ops.sigmoid_attention(q, layout, batch, cache, dim ** -0.5, window, keep, bias, got)
+    ops.sigmoid_attention(q, layout, batch, cache, dim ** -0.5, window, keep, bias, got, kernel=kernel)
     twin.sigmoid_attention(q, layout, batch, cache, dim ** -0.5, window, keep, bias, want)
     live = batch.seq_of_token >= 0
     close(got[live], want[live], dtype, "sigmoid attention", 2e-5, 8e-3)
@@ -222,7 +228,7 @@ def test_long_decoding_through_graphs(ops, dtype):
     name, lengths = "mix", (230,)
     requests = requests_for(name, lengths)
     steps, rows = replay_cases.decode_tail(requests, tail=200)
-    runner = make_runner(name, ops, "cuda", dtype, num_tokens=192, poison=False)
+    runner = make_runner(name, ops, "cuda", dtype, num_tokens=192, poison=False, max_model_len=256)
     replay_and_compare(runner, name, lengths, steps, rows, tolerance_for(dtype, name, lengths))
     assert runner.graph_replays > 100
 
