@@ -47,6 +47,12 @@ __device__ __forceinline__ void stage_float(float* dst, const float* src, bool t
     const int bytes = take ? 4 : 0;
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
+// Four floats at once (both addresses 16-byte aligned).
+__device__ __forceinline__ void stage_float4(float* dst, const float* src, bool take) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = take ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void stage_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void stage_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
@@ -627,7 +633,8 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
                           const float* __restrict__ decay_in, float decay_scale, float unit_eps,
                           float* __restrict__ cells, int64_t cell_stride,
                           const int* __restrict__ q_start, const int* __restrict__ slots,
-                          float* __restrict__ out, int heads, int dim, int vdim, int chunks_per_head) {
+                          float* __restrict__ out, int heads, int dim, int vdim, int chunks_per_head,
+                          int vec4) {
     grid_dependency_sync();
     extern __shared__ __align__(16) float sm[];
     constexpr int SL = SS_SLICES;
@@ -661,6 +668,27 @@ general_delta_scan_kernel(const float* __restrict__ pre, int ld, int at_r, int a
         float* w_to = a_to + TILE * DP;
         float* v_to = w_to + TILE * DP;
         const int nt = min(TILE, end - t0);
+        if (vec4) {
+            // every row, offset and size a multiple of four floats: 16 bytes a copy
+            for (int idx = tid; idx < nt * (DP / 4); idx += blockDim.x) {
+                const int tt = idx / (DP / 4), d = 4 * (idx - tt * (DP / 4));
+                const bool take = d < dim;
+                const float* row = pre + (int64_t)(t0 + tt) * ld + head * dim + d;
+                stage_float4(r_to + 4 * idx, take ? row + at_r : pre, take);
+                stage_float4(k_to + 4 * idx, take ? row + at_k : pre, take);
+                stage_float4(a_to + 4 * idx, take ? row + at_a : pre, take);
+                stage_float4(w_to + 4 * idx,
+                             take ? decay_in + (int64_t)(t0 + tt) * heads * dim + head * dim + d : pre, take);
+            }
+            for (int idx = tid; idx < nt * (cols / 4); idx += blockDim.x) {
+                const int tt = idx / (cols / 4), pp = chunk * cols + 4 * (idx - tt * (cols / 4));
+                const bool take = pp < vdim;
+                stage_float4(v_to + 4 * idx,
+                             take ? pre + (int64_t)(t0 + tt) * ld + at_v + head * vdim + pp : pre, take);
+            }
+            stage_commit();
+            return;
+        }
         for (int idx = tid; idx < nt * DP; idx += blockDim.x) {
             const int tt = idx / DP, d = idx - tt * DP;
             const bool take = d < dim;
@@ -1106,6 +1134,9 @@ MB_EXPORT int mb_general_delta_scan(const float* pre, int ld, int at_r, int at_k
     // the same whichever block holds it, so the result does not depend on the split)
     while (warps > 8 && (long long)heads * num_seqs * ((vdim + warps * 4 - 1) / (warps * 4)) < 148)
         warps /= 2;
+    const int vec4 = ld % 4 == 0 && at_r % 4 == 0 && at_k % 4 == 0 && at_v % 4 == 0 && at_a % 4 == 0 &&
+                     dim % 4 == 0 && vdim % 4 == 0 && ((uintptr_t)pre & 15) == 0 &&
+                     ((uintptr_t)decay_in & 15) == 0;
     const int cols = warps * 4;
     const int chunks = (vdim + cols - 1) / cols;
     dim3 grid(heads * chunks, num_seqs);
@@ -1119,11 +1150,11 @@ MB_EXPORT int mb_general_delta_scan(const float* pre, int ld, int at_r, int at_k
         if (precise)                                                                               \
             MB_LAUNCH((general_delta_scan_kernel<DPT, double, TILE>), grid, warps * 32, smem, s, pre, \
                       ld, at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,          \
-                      (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks);        \
+                      (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks, vec4);  \
         else                                                                                       \
             MB_LAUNCH((general_delta_scan_kernel<DPT, float, TILE>), grid, warps * 32, smem, s, pre, \
                       ld, at_r, at_k, at_v, at_a, decay_in, decay_scale, unit_eps, cells,          \
-                      (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks);        \
+                      (int64_t)cell_stride, q_start, slots, out, heads, dim, vdim, chunks, vec4);  \
     } while (0)
     // (the widest matrices stage 16 tokens at a time: two stages of 32 would not fit)
     if (dim <= 32) MB_GD_CASE(4, 32);
