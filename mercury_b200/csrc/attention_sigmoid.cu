@@ -266,12 +266,12 @@ int launch_sigmoid(const void* q, const void* k_pages, const void* v_pages, cons
                    cudaStream_t s) {
     const size_t smem = (size_t)(SG_ROWS * d + SG_KEYS * (d + 1) + SG_KEYS * d) * sizeof(float) +
                         SG_KEYS * sizeof(int);
-    static bool raised = false;
-    if (smem > 48 * 1024 && !raised) {
+    static size_t raised = 0;   // the most asked for so far (head sizes differ)
+    if (smem > 48 * 1024 && smem > raised) {
         if (cudaFuncSetAttribute(sigmoid_attention_kernel<T, NC>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
-        raised = true;
+        raised = smem;
     }
     dim3 grid(num_seqs * tiles_per_seq, n_kv, num_splits);
     MB_LAUNCH((sigmoid_attention_kernel<T, NC>), grid, SG_WARPS * 32, smem, s, (const T*)q,

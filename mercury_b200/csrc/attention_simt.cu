@@ -237,13 +237,13 @@ int launch_attention(const void* qkv, int q_row_stride, const void* k_pages, con
                      int num_splits, const float* sinks, cudaStream_t s) {
     const size_t smem = (size_t)(ATT_ROWS * d + ATT_KEYS * (d + 1) + ATT_KEYS * d) * sizeof(float) +
                         ATT_KEYS * sizeof(int);
-    static bool raised = false;  // one flag per instantiation
-    if (smem > 48 * 1024 && !raised) {
+    static size_t raised = 0;   // per instantiation: the most asked for so far (head sizes differ)
+    if (smem > 48 * 1024 && smem > raised) {
         if (cudaFuncSetAttribute(paged_attention_kernel<T, NC>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess)
             return MB_ERR_UNSUPPORTED_SIZE;
-        raised = true;
+        raised = smem;
     }
     dim3 grid(num_seqs * tiles_per_seq, n_kv, num_splits);
     MB_LAUNCH((paged_attention_kernel<T, NC>), grid, ATT_WARPS * 32, smem, s, 
