@@ -78,15 +78,31 @@ __global__ void softcap_kernel(float* __restrict__ x, int64_t total, float cap) 
 
 // A norm BEHIND two sublayers that ran side by side: d = a * delta + b * delta2 (delta2 may be
 // null), h <- h + d * rsqrt(mean(d^2) + eps) * w. One block per row, d kept in shared memory.
+// With a ring (the state of the convolution in front of the sublayer, [slots][span][hidden]),
+// the row of the stream as the sublayer found it is first kept there if it is among its
+// sequence's last `span` positions (at position modulo span): the kernel that read the ring
+// ran earlier on the stream, and this one sees the old row anyway.
 template <typename TD>
 __global__ void rmsnorm_add_pair_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                         const TD* __restrict__ delta2, float a, float b,
                                         const void* __restrict__ w, int w_dtype, float eps,
-                                        int hidden) {
+                                        int hidden, float* __restrict__ ring, int64_t ring_stride,
+                                        int span, const int* __restrict__ positions,
+                                        const int* __restrict__ seq_of_token,
+                                        const int* __restrict__ kv_len, const int* __restrict__ slots) {
     grid_dependency_sync();
     extern __shared__ float pair_row_s[];
     __shared__ float scratch[33];
     const int64_t at = (int64_t)blockIdx.x * hidden;
+    float* keep = nullptr;
+    if (ring != nullptr) {
+        const int seq = seq_of_token[blockIdx.x];
+        if (seq >= 0) {
+            const int pos = positions[blockIdx.x];
+            if (pos >= kv_len[seq] - span)
+                keep = ring + (int64_t)slots[seq] * ring_stride + (int64_t)(pos % span) * hidden;
+        }
+    }
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float d = a * to_float(delta[at + c]);
@@ -96,8 +112,11 @@ __global__ void rmsnorm_add_pair_kernel(float* __restrict__ h, const TD* __restr
     }
     ss = block_sum(ss, scratch);
     const float rstd = 1.f / sqrtf(ss / (float)hidden + eps);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
-        h[at + c] += pair_row_s[c] * rstd * load_as_float(w, c, w_dtype);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float old = h[at + c];
+        if (keep != nullptr) keep[c] = old;
+        h[at + c] = old + pair_row_s[c] * rstd * load_as_float(w, c, w_dtype);
+    }
 }
 
 // What a sublayer reads in place of the stream: out[t][c] = x[t][c] + sum_j w[c][j] *
@@ -222,8 +241,12 @@ MB_EXPORT int mb_softcap(float* x, long long total, float cap, void* stream) {
 // delta2 may be null (then b is not used); both deltas share `delta_dtype`.
 MB_EXPORT int mb_rmsnorm_add_pair(float* h, const void* delta, const void* delta2, int delta_dtype,
                                   float a, float b, const void* w, int w_dtype, float eps, int count,
-                                  int hidden, void* stream) {
+                                  int hidden, float* ring, long long ring_stride, int span,
+                                  const int* positions, const int* seq_of_token, const int* kv_len,
+                                  const int* slots, void* stream) {
     if (count <= 0 || hidden <= 0) return MB_OK;
+    if (ring != nullptr && (span <= 0 || !positions || !seq_of_token || !kv_len || !slots))
+        return MB_ERR_UNSUPPORTED_SIZE;
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 160 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -240,7 +263,8 @@ MB_EXPORT int mb_rmsnorm_add_pair(float* h, const void* delta, const void* delta
             raised = smem;                                                                        \
         }                                                                                         \
         MB_LAUNCH((rmsnorm_add_pair_kernel<TD>), count, threads, smem, s, h, (const TD*)delta,    \
-                  (const TD*)delta2, a, b, w, w_dtype, eps, hidden);                              \
+                  (const TD*)delta2, a, b, w, w_dtype, eps, hidden, ring, (int64_t)ring_stride,   \
+                  span, positions, seq_of_token, kv_len, slots);                                  \
     } while (0)
     if (delta_dtype == MB_F32) MB_RAP_CASE(float);
     else if (delta_dtype == MB_BF16) MB_RAP_CASE(bf);

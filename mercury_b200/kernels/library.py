@@ -145,7 +145,8 @@ _SIGNATURES = {
     "mb_expert_combine_sorted": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_expert_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_rmsnorm_add_pair": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int,
-                            c_float, c_int, c_int, c_void_p],
+                            c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p],
     "mb_stream_conv": [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_stream_tail_store": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,

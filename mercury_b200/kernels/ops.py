@@ -303,22 +303,31 @@ class CudaOps:
 
     @_timed("norm")
     def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out, delta2=None,
-                    scale=1.0, scale2=1.0):
+                    scale=1.0, scale2=1.0, tail=None):
         """h += rmsnorm(delta) * weight (a norm behind a sublayer); with `next_weight` also
         out = rmsnorm(h) * next_weight of the new stream, in the same kernel. With `delta2` or a
         `scale` the norm is taken of scale * delta + scale2 * delta2 (two sublayers that ran
         side by side)."""
         self._rows(h), self._rows(delta)
-        if delta2 is not None or scale != 1.0:
+        if delta2 is not None or scale != 1.0 or tail is not None:
             if next_weight is not None:
                 raise KernelError("rmsnorm_add: two deltas together with the next norm are not built")
             if delta2 is not None:
                 self._rows(delta2)
                 if delta2.dtype != delta.dtype or delta2.shape != delta.shape:
                     raise KernelError("rmsnorm_add: the two deltas differ in type or shape")
+            # `tail` = (ring, batch): the stream's rows as the sublayer found them, a sequence's
+            # last ones, go into the ring of the convolution in front of the sublayer
+            ring, batch = tail if tail is not None else (None, None)
             check(self.lib.mb_rmsnorm_add_pair(
                 _ptr(h), _ptr(delta), _ptr(delta2), _flag(delta.dtype), float(scale), float(scale2),
                 _ptr(weight), _flag(weight.dtype), float(eps), h.shape[0], h.shape[1],
+                _ptr(ring), ring.stride(0) if ring is not None else 0,
+                ring.shape[1] if ring is not None else 0,
+                _ptr(batch.positions) if ring is not None else None,
+                _ptr(batch.seq_of_token) if ring is not None else None,
+                _ptr(batch.kv_len) if ring is not None else None,
+                _ptr(batch.slots) if ring is not None else None,
                 self._stream()), "rmsnorm_add (pair)")
             self.launches += 1
             self._note_stream_write()

@@ -205,7 +205,10 @@ class PostNormBlock:
             raise ValueError("a post-norm block takes the stream with nothing pending")
         count = len(self._mixers)
         own = dict(zip(map(id, self.state_parts()), states[count:]))
-        x = self.mixer_input.forward(h, ctx, own.get(id(self.mixer_input)))
+        # the rings of the input convolutions are refilled by the norms behind the sublayers,
+        # which see the stream as the convolutions read it
+        ring = own.get(id(self.mixer_input))
+        x = self.mixer_input.forward(h, ctx, ring, store_tail=False)
         outs = []
         for index, mixer in enumerate(self._mixers):
             # mixers side by side leave their outputs in buffers of their own
@@ -213,16 +216,18 @@ class PostNormBlock:
             outs.append(mixer.forward(x, ctx, caches[index], states[index]))
         ctx.side = 0
         if count == 1 and self.mixer_scales[0] == 1.0:
-            self.mixer_post_norm.normed_add(h, outs[0], ctx)
+            self.mixer_post_norm.normed_add(h, outs[0], ctx, tail=ring)
         else:
             self.mixer_post_norm.normed_add(h, outs[0], ctx,
                                             second=outs[1] if count == 2 else None,
                                             scales=(self.mixer_scales[0],
-                                                    self.mixer_scales[1] if count == 2 else 0.0))
+                                                    self.mixer_scales[1] if count == 2 else 0.0),
+                                            tail=ring)
         if self.feed_forward is None:
             return None
-        x = self.feed_forward_input.forward(h, ctx, own.get(id(self.feed_forward_input)))
-        self.feed_forward_post_norm.normed_add(h, self.feed_forward.forward(x, ctx), ctx)
+        ring = own.get(id(self.feed_forward_input))
+        x = self.feed_forward_input.forward(h, ctx, ring, store_tail=False)
+        self.feed_forward_post_norm.normed_add(h, self.feed_forward.forward(x, ctx), ctx, tail=ring)
         return None
 
 

@@ -43,10 +43,13 @@ class InputConvolution(Part):
         # the convolution runs on the float32 stream, so its taps are float32 in both engines
         self.weight = setup.place(tensors[self.weight_name]).float().contiguous()
 
-    def forward(self, h, ctx, state):
+    def forward(self, h, ctx, state, store_tail: bool = True):
+        """`store_tail=False`: the caller keeps the step's last rows itself, before the stream
+        changes (the post-norm block hands the ring to the norm behind the sublayer, whose
+        kernel still sees the rows as they were read here)."""
         out = ctx.buffer("sublayer_in", h.shape[0], self.size)
         ctx.ops.stream_conv(h, self.weight, state, ctx.batch, out)
-        if state is not None:
+        if state is not None and store_tail:
             # behind the kernel that read the ring: the step's own last rows replace it
             ctx.ops.stream_tail_store(h, state, ctx.batch)
         return out
@@ -64,7 +67,7 @@ class StreamInput(Part):
     def state_need(self):
         return None
 
-    def forward(self, h, ctx, state):
+    def forward(self, h, ctx, state, store_tail: bool = True):
         out = ctx.buffer("sublayer_in", h.shape[0], self.size)
         ctx.ops.stream_conv(h, None, None, ctx.batch, out)
         return out

@@ -90,18 +90,24 @@ class RMSNorm(Norm):
             weight = (1.0 + weight.float()).contiguous()
         self.weight = weight
 
-    def normed_add(self, h, delta, ctx, then_norm=None, second=None, scales=None):
+    def normed_add(self, h, delta, ctx, then_norm=None, second=None, scales=None, tail=None):
         """h <- h + norm(delta): this norm applied to a sublayer's OUTPUT before it joins the
         float32 stream. With `then_norm` (an RMSNorm over the same width) the same kernel
         also leaves that norm's output of the new stream in `ctx.prenormed`. With `second`
         (the output of a mixer that ran beside the first) and `scales` (a, b) the norm is
-        taken of a * delta + b * second."""
+        taken of a * delta + b * second. With `tail` (the ring of the convolution the sublayer
+        read through) the same kernel first keeps the stream's rows as the sublayer found
+        them, each sequence's last ones, in that ring."""
         follow = then_norm if (isinstance(then_norm, RMSNorm) and then_norm.size == self.size) else None
+        if tail is not None:
+            follow = None                 # the kernel that keeps the rows does not norm ahead
         out = ctx.buffer("normed", h.shape[0], self.size) if follow is not None else None
         extra = {}
         if second is not None or scales is not None:
             a, b = scales if scales is not None else (1.0, 1.0)
             extra = {"delta2": second, "scale": float(a), "scale2": float(b)}
+        if tail is not None:
+            extra["tail"] = (tail, ctx.batch)
         ctx.ops.rmsnorm_add(h, delta, self.weight, self.eps,
                             follow.weight if follow is not None else None,
                             follow.eps if follow is not None else 0.0, out, **extra)

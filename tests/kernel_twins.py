@@ -26,7 +26,9 @@ class TorchOps:
         out.copy_(rows.to(out.dtype))
 
     def rmsnorm_add(self, h, delta, weight, eps, next_weight, next_eps, out, delta2=None,
-                    scale=1.0, scale2=1.0):
+                    scale=1.0, scale2=1.0, tail=None):
+        if tail is not None:
+            self.stream_tail_store(h, tail[0], tail[1])
         d = delta.to(self.acc)
         if delta2 is not None or scale != 1.0:
             d = d * scale

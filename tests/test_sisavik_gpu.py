@@ -82,10 +82,13 @@ def ragged(q_lens, kv_lens, slots=None, pad=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("fused", [False, True], ids=["store", "store-in-norm"])
 @pytest.mark.parametrize("width,taps", [(200, 3), (1024, 4), (72, 2), (136, 7)])
-def test_stream_convolution_over_steps(ops, twin, dtype, width, taps):
+def test_stream_convolution_over_steps(ops, twin, dtype, width, taps, fused):
     """Sequences in scattered slots over steps of unequal portions, shorter and longer than
-    the convolution's reach, one of them absent from a step; the ring carries over."""
+    the convolution's reach, one of them absent from a step; the ring carries over. `fused`:
+    the step's last rows are kept by the norm behind the sublayer, which then changes the
+    stream."""
     weight = rand((width, taps), torch.float32, 1, 0.5)
     state = torch.zeros((6, taps - 1, width), dtype=torch.float32, device="cuda")
     state_want = state.clone()
@@ -98,9 +101,20 @@ def test_stream_convolution_over_steps(ops, twin, dtype, width, taps):
         want = torch.zeros_like(got)
         ops.stream_conv(h, weight, state, batch, got)
         twin.stream_conv(h, weight, state_want, batch, want)
-        ops.stream_tail_store(h, state, batch)
-        twin.stream_tail_store(h, state_want, batch)
         live = batch.seq_of_token >= 0
+        if fused:
+            delta = rand((batch.num_tokens, width), dtype, 20 + step)
+            delta2 = rand((batch.num_tokens, width), dtype, 30 + step) if step % 2 else None
+            gain = rand((width,), torch.float32, 3) + 1
+            h_want = h.clone()
+            ops.rmsnorm_add(h, delta, gain, 1e-5, None, 0.0, None, delta2=delta2, scale=0.7,
+                            scale2=1.3, tail=(state, batch))
+            twin.rmsnorm_add(h_want, delta, gain, 1e-5, None, 0.0, None, delta2=delta2, scale=0.7,
+                             scale2=1.3, tail=(state_want, batch))
+            close(h[live], h_want[live], torch.float32, f"stream after step {step}")
+        else:
+            ops.stream_tail_store(h, state, batch)
+            twin.stream_tail_store(h, state_want, batch)
         close(got[live], want[live], dtype, f"step {step}")
         assert torch.equal(state, state_want), f"ring after step {step}"
         at = kv
@@ -131,7 +145,7 @@ def test_general_delta_scan_over_steps(ops, twin, heads, dim, vdim, precise):
 
 SIGMOID_CASES = [
     # heads, kv heads, dim, page, q_lens, kv_lens, window, keep
-    (4, 2, 64, 16, (5, 1, 33), (5, 140, 33), 72, 20),
+    (6, 3, 64, 16, (5, 1, 33), (5, 140, 33), 50, 13),
     (6, 2, 32, 16, (1, 1, 1, 1), (1, 9, 240, 400), 50, 7),
     (8, 8, 16, 8, (70, 2), (200, 66), 33, 0),
     (3, 1, 128, 32, (40, 1, 2), (100, 777, 50), 64, 64),
@@ -281,3 +295,50 @@ def test_greedy_generation_through_the_engine_and_cli(ops, tmp_path):
         capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stderr[-2000:]
     assert json.loads(done.stdout.strip().splitlines()[-1])["output_ids"] == greedy(stored_raw, stored, prompts[2], 5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program_on_a_model_folder(dtype, tmp_path):
+    """The replay program as a user runs it: a folder whose config.json does not name the
+    decay map's rows (the tensors give them), steps on standard input, a pool for the live
+    requests only."""
+    import copy
+    from pathlib import Path
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    name = "odd"
+    raw, _config, tensors = sisavik_model(name)
+    bare = copy.deepcopy(raw)
+    for layer in bare["layers"]:
+        if layer["type"] == "parallel":
+            del layer["mixer"]["right"]["decay_rank"]
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(bare))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    lengths = (50, 7, 121, 33, 90, 64)
+    requests = requests_for(name, lengths)
+    steps, rows = replay_cases.mixed(requests, 320, seed=2)
+    root = Path(__file__).resolve().parent.parent
+    out = tmp_path / "out"
+    done = subprocess.run(
+        [str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+         "--max-tokens", "320"],
+        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+        timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [l for l in done.stdout.split("\n") if l.startswith("done ")] == \
+        [f"done {s['step']}" for s in steps]
+    from sisavik_cases import oracle
+
+    want = oracle(name, lengths)
+    tol = tolerance_for(torch.float32 if dtype == "float32" else torch.bfloat16, name, lengths)
+    for step, expected in rows.items():
+        if not expected:
+            continue
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(expected), -1)
+        for row, (rid, pos) in enumerate(expected):
+            err = np.abs(got[row] - want[rid][pos]).max() / np.abs(want[rid]).max()
+            assert err <= tol, (step, rid, pos, err)
