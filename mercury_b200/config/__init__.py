@@ -10,6 +10,7 @@ from .model_config import (  # noqa: F401
     ConfigError,
     FegenexConfig,
     KinelixConfig,
+    LizazenConfig,
     ModelConfig,
     Qwen2Config,
     architecture_named,

@@ -549,6 +549,164 @@ def sisavik_sizes_from_tensors(raw: dict, shapes: dict) -> dict:
     return out
 
 
+# --------------------------------------------------------------------------- Lizazen
+
+@dataclass(frozen=True)
+class LizazenConfig(ModelConfig):
+    """A Lizazen decoder: a token row plus a row of a hashed bigram table opens the stream;
+    every layer has an RMS norm before and behind each sublayer. A layer's mixer is
+    `attention` (grouped-query attention with biased q/k projections, values that are the keys
+    as projected, one RMS norm over all heads' rows of q and of k, a partial rotation whose
+    long wavelengths are slowed down, scores under a tanh cap, a sliding window and a softmax
+    sink), `attention_2` (differential attention: two softmax maps per head over the same
+    values, a sliding window beside kept first tokens) or `parallel` (softmax attention over
+    chunks of positions beside retention, a linear attention with a fixed decay per head;
+    the two outputs are normed and averaged). The feed-forward is dense with clamped gate
+    and up (`kind: dense`), a mixture of experts whose router score multiplies the expert's
+    input, with a shared expert (`kind: moe`), or absent. config.json keys: `architecture`,
+    `width`, `vocab`, `norm.eps`, `embedding.bigram` (`buckets`, `mul_prev`, `mul_cur`; absent:
+    no bigram table) and `layers`, a list of `{"type", "mixer": {...}, "mlp": {...} | null}`.
+    Positions are bounded by `max_positions` alone (not a key of the design)."""
+
+    width: int
+    vocab: int
+    norm_eps: float
+    bigram: tuple | None = None          # (buckets, mul_prev, mul_cur)
+    max_positions: int = 1 << 20
+    layers: tuple = ()
+
+    DEFAULT_POSITIONS = 1 << 20
+    MIXERS = ("attention", "attention_2", "parallel")
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "LizazenConfig":
+        import copy
+
+        def need(table, key: str, where: str) -> Any:
+            if not isinstance(table, dict) or key not in table:
+                raise ConfigError(f"config.json has no {key!r} in {where}, which Lizazen needs")
+            return table[key]
+
+        def positive(table, key: str, where: str) -> int:
+            value = int(need(table, key, where))
+            if value <= 0:
+                raise ConfigError(f"{where}: {key}={value} must be positive")
+            return value
+
+        def rotation(table: dict, where: str) -> None:
+            rot = table.get("rot")
+            if not rot:
+                return
+            dims = int(need(rot, "dims", f"{where}'s rot"))
+            if dims < 0 or dims % 2 or dims > int(table["dim"]):
+                raise ConfigError(f"{where}: rot.dims={dims} must be even and at most {table['dim']}")
+            if dims and float(need(rot, "base", f"{where}'s rot")) <= 0:
+                raise ConfigError(f"{where}: rot.base must be positive")
+            scaling = rot.get("scaling")
+            if scaling:
+                for key in ("factor", "low", "high", "original"):
+                    if float(need(scaling, key, f"{where}'s rot.scaling")) <= 0:
+                        raise ConfigError(f"{where}: rot.scaling.{key} must be positive")
+                if float(scaling["high"]) == float(scaling["low"]):
+                    raise ConfigError(f"{where}: rot.scaling.high must differ from rot.scaling.low")
+
+        def attention(table: dict, where: str, keys=("heads", "kv_heads", "dim", "vdim")) -> None:
+            for key in keys:
+                positive(table, key, where)
+            float(need(table, "scale", where))
+            if int(table["heads"]) % int(table["kv_heads"]):
+                raise ConfigError(f"{where}: {table['heads']} query heads do not divide into "
+                                  f"{table['kv_heads']} key/value heads")
+            rotation(table, where)
+            positive(need(table, "mask", where), "size", f"{where}'s mask")
+            if int(table["mask"].get("keep_first", 0)) < 0:
+                raise ConfigError(f"{where}: mask.keep_first must not be negative")
+
+        def expert(table, where: str) -> None:
+            positive(table, "ff", where)
+
+        layers = []
+        for index, layer in enumerate(need(raw, "layers", "the model")):
+            where = f"layer {index}"
+            kind = need(layer, "type", where)
+            mixer = need(layer, "mixer", where)
+            if kind == "attention":
+                attention(mixer, f"{where}'s mixer")
+                if int(mixer["vdim"]) != int(mixer["dim"]):
+                    raise ConfigError(f"{where}: the values are the keys, so vdim={mixer['vdim']} "
+                                      f"must equal dim={mixer['dim']}")
+                if float(mixer.get("softcap") or 0.0) < 0:
+                    raise ConfigError(f"{where}: softcap must not be negative")
+            elif kind == "attention_2":
+                attention(mixer, f"{where}'s mixer")
+                float(need(mixer, "diff", f"{where}'s mixer"))
+            elif kind == "parallel":
+                attention(need(mixer, "left", f"{where}'s mixer"), f"{where}'s left mixer")
+                right = need(mixer, "right", f"{where}'s mixer")
+                for key in ("heads", "dim", "vdim"):
+                    positive(right, key, f"{where}'s right mixer")
+                rotation(right, f"{where}'s right mixer")
+                decay = need(right, "decay", f"{where}'s right mixer")
+                if len(decay) != int(right["heads"]):
+                    raise ConfigError(f"{where}: {len(decay)} decays for {right['heads']} heads")
+            else:
+                raise ConfigError(f"{where}: mixer type {kind!r} is not one of "
+                                  f"{', '.join(cls.MIXERS)}")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                form = need(mlp, "kind", f"{where}'s mlp")
+                if form == "dense":
+                    positive(mlp, "ff", f"{where}'s mlp")
+                    if float(need(mlp, "limit", f"{where}'s mlp")) <= 0:
+                        raise ConfigError(f"{where}: mlp.limit must be positive")
+                elif form == "moe":
+                    expert(need(mlp, "expert", f"{where}'s mlp"), f"{where}'s mlp.expert")
+                    router = need(mlp, "router", f"{where}'s mlp")
+                    experts = positive(router, "experts", f"{where}'s mlp.router")
+                    if not 1 <= positive(router, "top", f"{where}'s mlp.router") <= experts:
+                        raise ConfigError(f"{where}: top={router['top']} of {experts} experts")
+                    if mlp.get("shared") is not None:
+                        expert(mlp["shared"], f"{where}'s mlp.shared")
+                else:
+                    raise ConfigError(f"{where}: feed-forward kind {form!r} is neither dense nor moe")
+            layers.append({"type": kind, "mixer": copy.deepcopy(mixer), "mlp": copy.deepcopy(mlp)})
+        if not layers:
+            raise ConfigError("config.json lists no layers")
+        bigram = (raw.get("embedding") or {}).get("bigram")
+        if bigram:
+            bigram = (positive(bigram, "buckets", "embedding.bigram"),
+                      int(need(bigram, "mul_prev", "embedding.bigram")),
+                      int(need(bigram, "mul_cur", "embedding.bigram")))
+            if bigram[1] < 0 or bigram[2] < 0:
+                raise ConfigError("embedding.bigram: the multipliers must not be negative")
+        return cls(
+            architecture=str(raw.get("architecture") or (raw.get("architectures") or ["Lizazen"])[0]),
+            width=positive(raw, "width", "the model"),
+            vocab=positive(raw, "vocab", "the model"),
+            norm_eps=float(need(need(raw, "norm", "the model"), "eps", "norm")),
+            bigram=bigram or None,
+            max_positions=int(raw.get("max_positions") or cls.DEFAULT_POSITIONS),
+            layers=tuple(layers),
+        )
+
+    def to_dict(self) -> dict:
+        import copy
+
+        out = {
+            "architecture": self.architecture,
+            "width": self.width,
+            "vocab": self.vocab,
+            "norm": {"eps": self.norm_eps},
+            "layers": [copy.deepcopy(l) for l in self.layers],
+        }
+        if self.bigram:
+            out["embedding"] = {"bigram": {"buckets": self.bigram[0], "mul_prev": self.bigram[1],
+                                           "mul_cur": self.bigram[2]}}
+        if self.max_positions != self.DEFAULT_POSITIONS:
+            out["max_positions"] = self.max_positions
+        return out
+
+
 # --------------------------------------------------------------------------- the registry
 
 @dataclass(frozen=True)

@@ -24,6 +24,50 @@ __global__ void embed_kernel(const int* __restrict__ ids, const void* __restrict
         out[(int64_t)t * hidden + c] = ok ? load_as_float(table, base + c, table_dtype) : 0.f;
 }
 
+// A token row plus a row of a hashed table of token pairs: out[t, :] = table[ids[t], :] +
+// pairs[(prev * mul_prev + ids[t] * mul_cur) mod buckets, :], prev the token in front of t in
+// its sequence; a sequence's first token (position 0) takes row `buckets`, the table's last.
+// prev is the token in front within this step, or, for the first token a sequence brings to
+// this step, what the step before left in the sequence's state slot. The block of that first
+// token is also the one that leaves the step's last token there (nobody else touches the
+// slot, so the read and the write cannot meet).
+__global__ void embed_bigram_kernel(const int* __restrict__ ids, const void* __restrict__ table,
+                                    int table_dtype, const void* __restrict__ pairs, int pairs_dtype,
+                                    int buckets, int mul_prev, int mul_cur,
+                                    const int* __restrict__ positions,
+                                    const int* __restrict__ seq_of_token,
+                                    const int* __restrict__ q_start, const int* __restrict__ slots,
+                                    int* __restrict__ last_token, int64_t state_stride,
+                                    float* __restrict__ out, int hidden, int vocab) {
+    grid_dependency_sync();
+    const int t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    const int id = ids[t];
+    const bool ok = seq >= 0 && id >= 0 && id < vocab;
+#ifdef MB_BOUNDS_CHECK
+    if (seq >= 0 && !ok && threadIdx.x == 0) check_report(MB_CHECK_TOKEN, id, vocab);
+#endif
+    if (!ok) {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[(int64_t)t * hidden + c] = 0.f;
+        return;
+    }
+    const int begin = q_start[seq];
+    int* state = last_token + (int64_t)slots[seq] * state_stride;
+    int row = buckets;
+    if (positions[t] > 0) {
+        const int prev = t == begin ? state[0] : ids[t - 1];
+        row = (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % buckets);
+    }
+    const int64_t base = (int64_t)id * hidden, pbase = (int64_t)row * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        out[(int64_t)t * hidden + c] =
+            load_as_float(table, base + c, table_dtype) + load_as_float(pairs, pbase + c, pairs_dtype);
+    if (t == begin) {
+        __syncthreads();        // the slot has been read by now
+        if (threadIdx.x == 0) state[0] = ids[q_start[seq + 1] - 1];
+    }
+}
+
 // The same with a learned vector per position added: out[t, :] = table[ids[t], :] +
 // pos_table[positions[t], :], neither scaled.
 __global__ void embed_positions_kernel(const int* __restrict__ ids, const void* __restrict__ table,
@@ -85,10 +129,10 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ h, const TD* __restrict__
 }
 
 // out[t, i] = act(gate_up[t, i]) * gate_up[t, width + i]; act 0: SiLU, 1: the tanh form of
-// GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2: the clamped sigmoid gate below.
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t total,
-                                 int width, int act) {
+                                 int width, int act, float limit, float slope) {
     grid_dependency_sync();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -96,6 +140,13 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
         const int c = (int)(i - t * width);
         const float g = to_float(gate_up[t * 2 * width + c]);
         const float u = to_float(gate_up[t * 2 * width + width + c]);
+        if (act == 2) {
+            // a clamped sigmoid gate: g <- min(g, limit), u <- clamp(u, -limit, limit),
+            // g sigmoid(slope g) (u + 1)
+            const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+            out[i] = from_float<T>(gc / (1.f + expf(-slope * gc)) * (uc + 1.f));
+            continue;
+        }
         const float a = act == 0 ? g / (1.f + expf(-g))
                                  : 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
         out[i] = from_float<T>(a * u);
@@ -524,6 +575,19 @@ MB_EXPORT int mb_check_read(int* out, void* stream) {
     return MB_OK;
 }
 
+MB_EXPORT int mb_embed_bigram(const int* ids, const void* table, int table_dtype, const void* pairs,
+                              int pairs_dtype, int buckets, int mul_prev, int mul_cur,
+                              const int* positions, const int* seq_of_token, const int* q_start,
+                              const int* slots, int* last_token, long long state_stride, float* out,
+                              int tokens, int hidden, int vocab, void* stream) {
+    if (tokens <= 0) return MB_OK;
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0 || !last_token) return MB_ERR_UNSUPPORTED_SIZE;
+    MB_LAUNCH((embed_bigram_kernel), tokens, 256, 0, (cudaStream_t)stream, ids, table, table_dtype, pairs,
+              pairs_dtype, buckets, mul_prev, mul_cur, positions, seq_of_token, q_start, slots,
+              last_token, (int64_t)state_stride, out, hidden, vocab);
+    return launch_status();
+}
+
 MB_EXPORT int mb_embed(const int* ids, const void* table, int table_dtype, float* out, int tokens,
                        int hidden, int vocab, void* stream) {
     if (tokens <= 0) return MB_OK;
@@ -575,15 +639,15 @@ MB_EXPORT int mb_rmsnorm_add(float* h, const void* delta, int delta_dtype, const
 }
 
 MB_EXPORT int mb_gated_act(const void* gate_up, void* out, int tokens, int width, int dtype, int act,
-                           void* stream) {
+                           float limit, float slope, void* stream) {
     const int64_t total = (int64_t)tokens * width;
     if (total <= 0) return MB_OK;
-    if (act != 0 && act != 1) return MB_ERR_UNSUPPORTED_SIZE;
+    if (act < 0 || act > 2) return MB_ERR_UNSUPPORTED_SIZE;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == MB_F32)
         MB_LAUNCH((gated_act_kernel<float>), blocks, 256, 0, s, (const float*)gate_up, (float*)out, total,
-                  width, act);
+                  width, act, limit, slope);
     else if (dtype == MB_BF16 && act == 1 && width % 8 == 0) {
         const int64_t work = total / 8;
         const int grid = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
@@ -591,7 +655,7 @@ MB_EXPORT int mb_gated_act(const void* gate_up, void* out, int tokens, int width
                   (__nv_bfloat16*)out, tokens, width);
     } else if (dtype == MB_BF16)
         MB_LAUNCH((gated_act_kernel<__nv_bfloat16>), blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
-                  (__nv_bfloat16*)out, total, width, act);
+                  (__nv_bfloat16*)out, total, width, act, limit, slope);
     else
         return MB_ERR_BAD_DTYPE;
     return launch_status();

@@ -235,7 +235,7 @@ expert_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int c
 // thread (hidden a multiple of 8).
 __global__ void expert_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ perm,
                                      __nv_bfloat16* __restrict__ sorted, int pairs, int top,
-                                     int hidden) {
+                                     int hidden, const float* __restrict__ row_scale) {
     grid_dependency_sync();
     const int chunks = hidden / 8;
     const int64_t total = (int64_t)pairs * chunks;
@@ -244,8 +244,17 @@ __global__ void expert_gather_kernel(const __nv_bfloat16* __restrict__ x, const 
         const int64_t r = i / chunks;
         const int c = (int)(i - r * chunks);
         const int t = perm[r] / top;
-        reinterpret_cast<uint4*>(sorted + r * hidden)[c] =
-            reinterpret_cast<const uint4*>(x + (int64_t)t * hidden)[c];
+        uint4 piece = reinterpret_cast<const uint4*>(x + (int64_t)t * hidden)[c];
+        if (row_scale != nullptr) {       // a weight on the expert's input: the row times it
+            const float rs = row_scale[perm[r]];
+            __nv_bfloat162* two = reinterpret_cast<__nv_bfloat162*>(&piece);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 v = __bfloat1622float2(two[j]);
+                two[j] = __floats2bfloat162_rn(v.x * rs, v.y * rs);
+            }
+        }
+        reinterpret_cast<uint4*>(sorted + r * hidden)[c] = piece;
     }
 }
 
@@ -263,7 +272,7 @@ __global__ void expert_combine_sorted_kernel(const __nv_bfloat16* __restrict__ y
         const int n = (int)(i - t * hidden);
         float acc = 0.f;
         for (int j = 0; j < top; ++j)
-            acc = fmaf(weights[t * top + j],
+            acc = fmaf(weights != nullptr ? weights[t * top + j] : 1.f,
                        __bfloat162float(y[(int64_t)place[t * top + j] * hidden + n]), acc);
         out[i] = acc;
     }
@@ -277,7 +286,7 @@ template <typename TA, typename TW, int MODE>
 __global__ void __launch_bounds__(256)
 expert_product_kernel(const TA* __restrict__ a, int a_ld, const TW* __restrict__ w,
                       void* __restrict__ out, const int* __restrict__ plan, int cap, int top,
-                      int K, int N) {
+                      int K, int N, const float* __restrict__ row_scale) {
     grid_dependency_sync();
     const int tile = blockIdx.x;
     if (tile >= plan[0]) return;
@@ -357,7 +366,9 @@ expert_product_kernel(const TA* __restrict__ a, int a_ld, const TW* __restrict__
             const int n = n0 + tx * 4 + c;
             if (n >= N) continue;
             if (MODE == 0) {
-                const float g = acc[0][r][c], u = acc[PARTS - 1][r][c];
+                // a weight on the expert's INPUT scales both products (they have no bias)
+                const float rs = row_scale != nullptr ? row_scale[perm[row0 + lr]] : 1.f;
+                const float g = acc[0][r][c] * rs, u = acc[PARTS - 1][r][c] * rs;
                 reinterpret_cast<TA*>(out)[(int64_t)(row0 + lr) * N + n] =
                     from_float<TA>(g / (1.f + expf(-g)) * u);
             } else {
@@ -403,7 +414,8 @@ template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS)
 expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
                           const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
-                          const int* __restrict__ plan, int cap, int top, int K, int N) {
+                          const int* __restrict__ plan, int cap, int top, int K, int N,
+                          const float* __restrict__ row_scale) {
     grid_dependency_sync();
     const int tile = blockIdx.x;
     if (tile >= plan[0]) return;
@@ -515,13 +527,14 @@ expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
             const int lr = wr * 32 + i * 16 + g + h * 8;
             if (lr >= rows) continue;
             const int64_t dst_row = MODE == 0 ? (int64_t)(row0 + lr) : (int64_t)perm[row0 + lr];
+            const float rs = (MODE == 0 && row_scale != nullptr) ? row_scale[perm[row0 + lr]] : 1.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int n = n0 + wc * 32 + j * 8 + 2 * t4;
                 if (n >= N) continue;
-                const float v0 = acc[0][i][j][2 * h], v1 = acc[0][i][j][2 * h + 1];
+                const float v0 = acc[0][i][j][2 * h] * rs, v1 = acc[0][i][j][2 * h + 1] * rs;
                 if (MODE == 0) {
-                    const float u0 = acc[PARTS - 1][i][j][2 * h], u1 = acc[PARTS - 1][i][j][2 * h + 1];
+                    const float u0 = acc[PARTS - 1][i][j][2 * h] * rs, u1 = acc[PARTS - 1][i][j][2 * h + 1] * rs;
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + dst_row * N + n;
                     const float r0 = v0 / (1.f + expf(-v0)) * u0, r1 = v1 / (1.f + expf(-v1)) * u1;
                     if (n + 1 < N && (N & 1) == 0)
@@ -546,7 +559,7 @@ expert_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_ld,
 
 template <int MODE>
 int launch_expert_product_mma(const void* a, int a_ld, const void* w, void* out, const int* plan,
-                              int cap, int top, int K, int N, cudaStream_t s) {
+                              int cap, int top, int K, int N, const float* row_scale, cudaStream_t s) {
     constexpr int PARTS = MODE == 0 ? 2 : 1;
     const size_t smem = (size_t)TC_STAGES * (TC_BM + PARTS * TC_BN) * TC_BK * sizeof(__nv_bfloat16);
     // (with the kernel's static shared memory this is beyond the 48 KB a launch gets unasked)
@@ -560,11 +573,11 @@ int launch_expert_product_mma(const void* a, int a_ld, const void* w, void* out,
     dim3 grid(cap, (N + TC_BN - 1) / TC_BN);
     if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     MB_LAUNCH((expert_product_mma_kernel<MODE>), grid, TC_THREADS, smem, s, (const __nv_bfloat16*)a, a_ld,
-              (const __nv_bfloat16*)w, out, plan, cap, top, K, N);
+              (const __nv_bfloat16*)w, out, plan, cap, top, K, N, row_scale);
     return launch_status();
 }
 
-// out[t][n] = sum_j weights[t][j] * y[t * top + j][n], j ascending.
+// out[t][n] = sum_j weights[t][j] * y[t * top + j][n], j ascending (weights null: ones).
 __global__ void expert_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
                                       float* __restrict__ out, int tokens, int top, int hidden) {
     grid_dependency_sync();
@@ -575,22 +588,23 @@ __global__ void expert_combine_kernel(const float* __restrict__ y, const float* 
         const int n = (int)(i - t * hidden);
         float acc = 0.f;
         for (int j = 0; j < top; ++j)
-            acc = fmaf(weights[t * top + j], y[(t * top + j) * hidden + n], acc);
+            acc = fmaf(weights != nullptr ? weights[t * top + j] : 1.f, y[(t * top + j) * hidden + n], acc);
         out[i] = acc;
     }
 }
 
 template <typename TA, typename TW>
 int launch_expert_product(int mode, const void* a, int a_ld, const void* w, void* out,
-                          const int* plan, int cap, int top, int K, int N, cudaStream_t s) {
+                          const int* plan, int cap, int top, int K, int N, const float* row_scale,
+                          cudaStream_t s) {
     dim3 grid(cap, (N + EX_BN - 1) / EX_BN);
     if (grid.y > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     if (mode == 0)
         MB_LAUNCH((expert_product_kernel<TA, TW, 0>), grid, 256, 0, s, (const TA*)a, a_ld, (const TW*)w,
-                  out, plan, cap, top, K, N);
+                  out, plan, cap, top, K, N, row_scale);
     else
         MB_LAUNCH((expert_product_kernel<TA, TW, 1>), grid, 256, 0, s, (const TA*)a, a_ld, (const TW*)w,
-                  out, plan, cap, top, K, N);
+                  out, plan, cap, top, K, N, row_scale);
     return launch_status();
 }
 
@@ -677,33 +691,33 @@ MB_EXPORT int mb_expert_plan(const int* chosen, int pairs, int experts, int cap,
 // `bm`: the tile height the plan was made with (mb_expert_tile_rows), which names the kernel.
 MB_EXPORT int mb_expert_product(int mode, const void* a, int a_ld, const void* w, void* out,
                                 const int* plan, int cap, int top, int K, int N, int dtype, int bm,
-                                void* stream) {
+                                const float* row_scale, void* stream) {
     if (cap <= 0) return MB_OK;
     if (K <= 0 || N <= 0 || (mode != 0 && mode != 1)) return MB_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (bm == TC_BM) {
         if (dtype != MB_BF16 || K % 8 || a_ld % 8 || (((uintptr_t)a | (uintptr_t)w) & 15))
             return MB_ERR_ALIGNMENT;
-        return mode == 0 ? launch_expert_product_mma<0>(a, a_ld, w, out, plan, cap, top, K, N, s)
-                         : launch_expert_product_mma<1>(a, a_ld, w, out, plan, cap, top, K, N, s);
+        return mode == 0 ? launch_expert_product_mma<0>(a, a_ld, w, out, plan, cap, top, K, N, row_scale, s)
+                         : launch_expert_product_mma<1>(a, a_ld, w, out, plan, cap, top, K, N, nullptr, s);
     }
     if (bm != EX_BM) return MB_ERR_UNSUPPORTED_SIZE;
     if (dtype == MB_F32)
-        return launch_expert_product<float, float>(mode, a, a_ld, w, out, plan, cap, top, K, N, s);
+        return launch_expert_product<float, float>(mode, a, a_ld, w, out, plan, cap, top, K, N, row_scale, s);
     if (dtype == MB_BF16)
         return launch_expert_product<__nv_bfloat16, __nv_bfloat16>(mode, a, a_ld, w, out, plan, cap, top,
-                                                                   K, N, s);
+                                                                   K, N, row_scale, s);
     return MB_ERR_BAD_DTYPE;
 }
 
 MB_EXPORT int mb_expert_gather(const void* x, const int* perm, void* sorted, int pairs, int top,
-                               int hidden, void* stream) {
+                               int hidden, const float* row_scale, void* stream) {
     if (pairs <= 0) return MB_OK;
     if (hidden % 8 || (((uintptr_t)x | (uintptr_t)sorted) & 15)) return MB_ERR_ALIGNMENT;
     const long long want = ((long long)pairs * (hidden / 8) + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     MB_LAUNCH((expert_gather_kernel), blocks, 256, 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, perm,
-              (__nv_bfloat16*)sorted, pairs, top, hidden);
+              (__nv_bfloat16*)sorted, pairs, top, hidden, row_scale);
     return launch_status();
 }
 

@@ -119,6 +119,58 @@ __global__ void rmsnorm_add_pair_kernel(float* __restrict__ h, const TD* __restr
     }
 }
 
+// Two sublayer outputs that ran side by side, each under an RMS norm of its own, joined and
+// sent through the norm behind the sublayer: with n(x) = x * rsqrt(mean(x^2) + eps) * wx (or x
+// itself where wx is null), z = a n(x) + b n(y), h <- h + z * rsqrt(mean(z^2) + eps) * w, and,
+// when the norm that follows is given, out = h * rsqrt(mean(h^2) + eps2) * w2 of the new h in
+// the same pass. One block per row, the rows kept in shared memory between the sums. All
+// weights float32.
+template <typename TD, typename TO>
+__global__ void rmsnorm_join_add_kernel(float* __restrict__ h, const TD* __restrict__ x,
+                                        const TD* __restrict__ y, const float* __restrict__ wx,
+                                        const float* __restrict__ wy, float a, float b,
+                                        const float* __restrict__ w, float eps,
+                                        const float* __restrict__ w2, float eps2,
+                                        TO* __restrict__ out, int hidden) {
+    grid_dependency_sync();
+    extern __shared__ float join_s[];
+    float* x_s = join_s;
+    float* y_s = join_s + hidden;
+    __shared__ float scratch[33];
+    const int64_t at = (int64_t)blockIdx.x * hidden;
+    float sx = 0.f, sy = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float xv = to_float(x[at + c]), yv = to_float(y[at + c]);
+        x_s[c] = xv;
+        y_s[c] = yv;
+        sx = fmaf(xv, xv, sx);
+        sy = fmaf(yv, yv, sy);
+    }
+    float rx = 1.f, ry = 1.f;
+    if (wx != nullptr) rx = 1.f / sqrtf(block_sum(sx, scratch) / (float)hidden + eps);
+    if (wy != nullptr) ry = 1.f / sqrtf(block_sum(sy, scratch) / (float)hidden + eps);
+    float sz = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float xn = wx != nullptr ? x_s[c] * rx * wx[c] : x_s[c];
+        const float yn = wy != nullptr ? y_s[c] * ry * wy[c] : y_s[c];
+        const float z = fmaf(b, yn, a * xn);
+        x_s[c] = z;
+        sz = fmaf(z, z, sz);
+    }
+    const float rz = 1.f / sqrtf(block_sum(sz, scratch) / (float)hidden + eps);
+    float sh = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = h[at + c] + x_s[c] * rz * w[c];
+        h[at + c] = v;
+        y_s[c] = v;
+        sh = fmaf(v, v, sh);
+    }
+    if (w2 == nullptr) return;
+    const float rh = 1.f / sqrtf(block_sum(sh, scratch) / (float)hidden + eps2);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        out[at + c] = from_float<TO>(y_s[c] * rh * w2[c]);
+}
+
 // What a sublayer reads in place of the stream: out[t][c] = x[t][c] + sum_j w[c][j] *
 // x(p - taps + 1 + j)[c], where x(q) is the stream's row at position q of the token's
 // sequence: zero for q < 0, a row of this step for q >= first (the position of the
@@ -270,6 +322,43 @@ MB_EXPORT int mb_rmsnorm_add_pair(float* h, const void* delta, const void* delta
     else if (delta_dtype == MB_BF16) MB_RAP_CASE(bf);
     else return MB_ERR_BAD_DTYPE;
 #undef MB_RAP_CASE
+    return launch_status();
+}
+
+// x, y: [count][hidden] of x_dtype; wx, wy (null: that side is not normed), w and w2 (null: no
+// norm computed ahead) float32 [hidden]; out of out_dtype.
+MB_EXPORT int mb_rmsnorm_join_add(float* h, const void* x, const void* y, int x_dtype, const float* wx,
+                                  const float* wy, float a, float b, const float* w, float eps,
+                                  const float* w2, float eps2, void* out, int out_dtype, int count,
+                                  int hidden, void* stream) {
+    if (count <= 0 || hidden <= 0) return MB_OK;
+    if (!x || !y || !w || (w2 != nullptr && !out)) return MB_ERR_UNSUPPORTED_SIZE;
+    const size_t smem = (size_t)2 * hidden * sizeof(float);
+    if (smem > 160 * 1024) return MB_ERR_UNSUPPORTED_SIZE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define MB_RJ_CASE(TD, TO)                                                                        \
+    do {                                                                                          \
+        static size_t raised = 0;                                                                 \
+        if (smem + 256 > 48 * 1024 && smem > raised) {                                            \
+            if (cudaFuncSetAttribute(rmsnorm_join_add_kernel<TD, TO>,                             \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=   \
+                cudaSuccess)                                                                      \
+                return MB_ERR_UNSUPPORTED_SIZE;                                                   \
+            raised = smem;                                                                        \
+        }                                                                                         \
+        MB_LAUNCH((rmsnorm_join_add_kernel<TD, TO>), count, threads, smem, s, h, (const TD*)x,    \
+                  (const TD*)y, wx, wy, a, b, w, eps, w2, eps2, (TO*)out, hidden);                \
+    } while (0)
+    const bool wide_out = w2 == nullptr || out_dtype == MB_F32;
+    if (w2 != nullptr && out_dtype != MB_F32 && out_dtype != MB_BF16) return MB_ERR_BAD_DTYPE;
+    if (x_dtype == MB_F32 && wide_out) MB_RJ_CASE(float, float);
+    else if (x_dtype == MB_F32) MB_RJ_CASE(float, bf);
+    else if (x_dtype == MB_BF16 && wide_out) MB_RJ_CASE(bf, float);
+    else if (x_dtype == MB_BF16) MB_RJ_CASE(bf, bf);
+    else return MB_ERR_BAD_DTYPE;
+#undef MB_RJ_CASE
     return launch_status();
 }
 

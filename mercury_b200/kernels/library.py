@@ -88,7 +88,7 @@ _SIGNATURES = {
                            c_int, c_int, c_int, c_void_p],
     "mb_rmsnorm_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_float,
                        c_void_p, c_int, c_int, c_int, c_void_p],
-    "mb_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "mb_mixed_head_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int,
@@ -140,8 +140,24 @@ _SIGNATURES = {
     "mb_expert_tile_cap": [c_int, c_int, c_int],
     "mb_expert_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mb_expert_product": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                          c_int, c_int, c_int, c_void_p],
-    "mb_expert_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                          c_int, c_int, c_int, c_void_p, c_void_p],
+    "mb_expert_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mb_embed_bigram": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int,
+                        c_int, c_void_p],
+    "mb_rmsnorm_join_add": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float,
+                            c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int, c_int,
+                            c_void_p],
+    "mb_masked_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                          c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mb_masked_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int,
+                            c_float, c_float, c_float, c_int, c_int, c_void_p],
+    "mb_retention_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                          c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_int, c_void_p],
     "mb_expert_combine_sorted": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_expert_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mb_rmsnorm_add_pair": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int,
@@ -220,6 +236,8 @@ def load():
     lib.mb_sigmoid_attention_mma_supports.restype = c_int
     lib.mb_sigmoid_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_sigmoid_attention_scratch_floats.restype = c_longlong
+    lib.mb_masked_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.mb_masked_attention_scratch_floats.restype = c_longlong
     _LIB = lib
     return lib
 

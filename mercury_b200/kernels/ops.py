@@ -340,6 +340,42 @@ class CudaOps:
         self.launches += 1
         self._note_stream_write()
 
+    @_timed("embedding")
+    def embed_bigram(self, token_ids, table, pairs, buckets, mul_prev, mul_cur, state, batch, out):
+        """out = table[token] + pairs[(previous * mul_prev + token * mul_cur) mod buckets] (row
+        `buckets` for a sequence's first token) in the float32 stream; `state` [slots, 1] int32
+        holds every live sequence's last token and is brought up to date."""
+        self._rows(out)
+        if state.dtype != torch.int32 or pairs.shape[0] != buckets + 1:
+            raise KernelError("embed_bigram: the state is int32 and the pair table has buckets + 1 rows")
+        check(self.lib.mb_embed_bigram(
+            _ptr(token_ids), _ptr(table), _flag(table.dtype), _ptr(pairs), _flag(pairs.dtype),
+            int(buckets), int(mul_prev), int(mul_cur), _ptr(batch.positions), _ptr(batch.seq_of_token),
+            _ptr(batch.q_start), _ptr(batch.slots), _ptr(state), state.stride(0), _ptr(out),
+            out.shape[0], out.shape[1], table.shape[0], self._stream()), "embed_bigram")
+        self.launches += 1
+        self._note_stream_write()
+
+    @_timed("norm")
+    def rmsnorm_join_add(self, h, x, y, wx, wy, a, b, weight, eps, next_weight, next_eps, out):
+        """h += rmsnorm(a n(x) + b n(y)) * weight with n(x) = rmsnorm(x) * wx (x itself where wx is
+        None), likewise n(y): two sublayer outputs that ran side by side, normed each, joined,
+        and the norm behind the sublayer, in one pass. With `next_weight` also out = rmsnorm(h) *
+        next_weight of the new stream. All weights float32."""
+        self._rows(h), self._rows(x), self._rows(y)
+        if x.dtype != y.dtype or x.shape != y.shape:
+            raise KernelError("rmsnorm_join_add: the two outputs differ in type or shape")
+        for w in (wx, wy, weight, next_weight):
+            if w is not None and w.dtype != torch.float32:
+                raise KernelError("rmsnorm_join_add: the norm weights are float32")
+        check(self.lib.mb_rmsnorm_join_add(
+            _ptr(h), _ptr(x), _ptr(y), _flag(x.dtype), _ptr(wx), _ptr(wy), float(a), float(b),
+            _ptr(weight), float(eps), _ptr(next_weight), float(next_eps), _ptr(out),
+            _flag(out.dtype) if out is not None else 0, h.shape[0], h.shape[1], self._stream()),
+            "rmsnorm_join_add")
+        self.launches += 1
+        self._note_stream_write()
+
     def _note_stream_write(self) -> None:
         self._last_stream_write = self.launches + self.library_calls
 
@@ -581,24 +617,28 @@ class CudaOps:
         self.linear(x, weight, None, gate_up)
         self.swiglu(gate_up, out)
 
-    def linear_gated(self, x, weight, out, ctx, activation):
+    def linear_gated(self, x, weight, out, ctx, activation, limit=0.0, slope=1.0):
         """out = act(x . gate^T) * (x . up^T) for `weight` = [gate rows; up rows]; "silu" takes
         the fused kernels of `linear_swiglu`, "gelu_tanh" the product followed by the gate
-        kernel."""
+        kernel; "clamped_sigmoid" is g sigmoid(slope g) (u + 1) of g = min(gate, limit) and u =
+        clamp(up, -limit, limit), product and gate kernel as well."""
         if activation == "silu":
             return self.linear_swiglu(x, weight, out, ctx)
-        if activation != "gelu_tanh":
+        if activation not in ("gelu_tanh", "clamped_sigmoid"):
             raise KernelError(f"no gate kernel for the activation {activation!r}")
+        if self._pending(x) is not None:
+            x = x.materialize()
         m, width = x.shape[0], out.shape[1]
         gate_up = ctx.buffer("gate_up", m, 2 * width)
         with self._as("gated product"):
             self.linear(x, weight, None, gate_up)
-        self.gated_act(gate_up, out, 1)
+        self.gated_act(gate_up, out, 1 if activation == "gelu_tanh" else 2, limit, slope)
 
     @_timed("gate")
-    def gated_act(self, gate_up, out, act: int):
+    def gated_act(self, gate_up, out, act: int, limit: float = 0.0, slope: float = 1.0):
         check(self.lib.mb_gated_act(_ptr(gate_up), _ptr(out), out.shape[0], out.shape[1],
-                                    _flag(out.dtype), int(act), self._stream()), "gated_act")
+                                    _flag(out.dtype), int(act), float(limit), float(slope),
+                                    self._stream()), "gated_act")
         self.launches += 1
 
     # ------------------------------------------------------------------ recurrent mixers
@@ -890,6 +930,91 @@ class CudaOps:
                   "sigmoid_attention")
         self.launches += 1 if splits == 1 else 2
 
+    # ------------------------------------------------------------------ masked attention
+
+    MASK_KINDS = {"full": 0, "sliding": 1, "chunked": 2}
+
+    @_timed("rotary + store")
+    def masked_prepare(self, pre, layout, q_norm, k_norm, eps, tables, pairing, batch, cache, q,
+                       values_from_keys):
+        """pre = [q | k (| v)] float32, layout (heads, kv_heads, maps, dim, vdim): one RMS norm over
+        all of q's rows and one over all of k's (weights float32 over the whole projection, or
+        None), the rotation of the first numbers of every map of every head, q into `q`, keys
+        and values into the pages; with `values_from_keys` the values are the keys as projected."""
+        heads, kv_heads, maps, dim, vdim = layout
+        self._check_limits(cache, tables)
+        cos, sin = tables if tables is not None else (None, None)
+        rot = 2 * cos.shape[1] if cos is not None else 0
+        if q.dtype != cache.k.dtype or cache.v.dtype != cache.k.dtype:
+            raise KernelError("masked_prepare: pages and activations differ in dtype")
+        check(self.lib.mb_masked_prepare(
+            _ptr(pre), pre.shape[1], _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(cos), _ptr(sin), rot,
+            int(pairing == "interleaved"), _ptr(batch.positions), _ptr(batch.seq_of_token),
+            _ptr(cache.table), cache.table.shape[1], _ptr(cache.k), _ptr(cache.v), _ptr(q), heads,
+            kv_heads, maps, dim, vdim, int(bool(values_from_keys)), cache.page_size, pre.shape[0],
+            _flag(q.dtype), self._stream()), "masked_prepare")
+        self.launches += 1
+
+    @_timed("attention")
+    def masked_attention(self, q, layout, batch, cache, scale, mask, out, softcap=0.0, sinks=None,
+                         lam=0.0, sub_eps=0.0, out_scale=1.0, kernel: str | None = None):
+        """Softmax attention under `mask` = (kind, size, keep_first), kind "full", "sliding" or
+        "chunked": position p sees j <= p with j >= lo(p) or j < keep_first, lo(p) = 0, p - size +
+        1 or floor(p / size) * size. Scores q . k * scale, under softcap * tanh(. / softcap) when
+        softcap > 0; `sinks` [heads] float32 join the denominators. With maps = 2 in the layout
+        (heads, kv_heads, maps, dim, vdim) a head is two maps over the same values and its
+        output (a1 - lam a2) / rms(.) * out_scale (`sub_eps` inside the root)."""
+        heads, kv_heads, maps, dim, vdim = layout
+        kind, size, keep_first = mask
+        self._check_limits(cache)
+        tokens = q.shape[0]
+        group = heads // kv_heads
+        if getattr(batch, "attention_splits", None):
+            splits = batch.attention_splits
+        else:
+            reach = batch.max_kv_len if kind == "full" else min(
+                batch.max_kv_len, size + keep_first + batch.max_q_len)
+            tiles = -(-batch.max_q_len * group // 16)
+            blocks = batch.num_seqs * tiles * kv_heads
+            key_tiles = -(-reach // 32)
+            splits = 1
+            if blocks < self.sm_count and key_tiles >= 4:
+                splits = max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
+        floats = self.lib.mb_masked_attention_scratch_floats(tokens, heads, maps, vdim, splits)
+        scratch = self._scratch_for(floats) if floats else None
+        check(self.lib.mb_masked_attention(
+            _ptr(q), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), cache.table.shape[1],
+            _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token), _ptr(sinks), _ptr(out),
+            _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens, batch.num_seqs,
+            batch.max_q_len, heads, kv_heads, maps, dim, vdim, cache.page_size, float(scale),
+            float(softcap), self.MASK_KINDS[kind], int(size), int(keep_first), float(lam),
+            float(sub_eps), float(out_scale), splits, _flag(q.dtype), self._stream()),
+            "masked_attention")
+        self.launches += 1 if splits == 1 else 2
+
+    # ------------------------------------------------------------------ retention
+
+    @_timed("recurrence")
+    def retention_scan(self, pre, offsets, decay, key_scale, layout, tables, pairing, cells, batch, o):
+        """Per head S <- decay_h S + k v^T, o = S^T q, with q and k rotated by the token's position
+        (`tables`, or None) and k then times `key_scale`; q, k and v are read off `pre` (float32) at
+        `offsets`; `cells` [slots, heads * vdim * dim] float32 holds the matrices column by column;
+        `o` [tokens, heads * vdim] float32."""
+        heads, dim, vdim = layout
+        at_q, at_k, at_v = offsets
+        if pre.dtype != torch.float32 or o.dtype != torch.float32 or cells.dtype != torch.float32:
+            raise KernelError("retention_scan: inputs, matrices and read-outs are float32")
+        cos, sin = tables if tables is not None else (None, None)
+        rot = 2 * cos.shape[1] if cos is not None else 0
+        if tables is not None:
+            self._check_limits(None, tables)
+        check(self.lib.mb_retention_scan(
+            _ptr(pre), pre.shape[1], int(at_q), int(at_k), int(at_v), _ptr(decay), float(key_scale),
+            _ptr(cos), _ptr(sin), rot, int(pairing == "interleaved"), _ptr(batch.positions),
+            _ptr(cells), cells.stride(0), _ptr(batch.q_start), _ptr(batch.slots), _ptr(o),
+            batch.num_seqs, heads, dim, vdim, self._stream()), "retention_scan")
+        self.launches += 1
+
     # ------------------------------------------------------------------ latent attention
 
     @_timed("rotary + store")
@@ -989,10 +1114,13 @@ class CudaOps:
         self.launches += 1 if fused else 2
 
     @_timed("expert products")
-    def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx):
+    def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx, weight_on="output"):
         """out[t] = sum_j weights[t, j] * down[e] (silu(gate[e] x[t]) * (up[e] x[t])), e =
         chosen[t, j]: the step's (token, choice) pairs sorted by expert, two grouped products,
-        and the weighted sum in the order of the choice."""
+        and the weighted sum in the order of the choice. `weight_on` "input": the weight
+        multiplies what the expert reads instead, out[t] = sum_j expert_e(weights[t, j] x[t]); the
+        experts have no biases, so the weight is applied to both first products' results (or to
+        the gathered rows, where the library multiplies) and the sum is unweighted."""
         if self._pending(x) is not None:
             x = x.materialize()
         tokens, top = chosen.shape
@@ -1008,22 +1136,27 @@ class CudaOps:
         if (self.expert_library and self._grouped_mm is not None and x.dtype == torch.bfloat16
                 and gate_up.dtype == torch.bfloat16 and down.dtype == torch.bfloat16
                 and pairs >= self.expert_library_min_pairs and hidden % 8 == 0 and ff % 8 == 0):
-            return self._expert_library(x, weights, gate_up, down, out, ctx, plan, cap, tokens, top)
+            return self._expert_library(x, weights, gate_up, down, out, ctx, plan, cap, tokens, top,
+                                        weight_on)
         act = ctx.buffer("expert_act", pairs, ff)
         if act.dtype != x.dtype or gate_up.dtype != x.dtype or down.dtype != x.dtype:
             raise KernelError("expert_feed_forward: activations and expert matrices differ in dtype")
+        on_input = weight_on == "input"
         check(self.lib.mb_expert_product(0, _ptr(x), x.shape[1], _ptr(gate_up), _ptr(act), _ptr(plan),
-                                         cap, top, hidden, ff, _flag(x.dtype), bm, self._stream()),
+                                         cap, top, hidden, ff, _flag(x.dtype), bm,
+                                         _ptr(weights) if on_input else None, self._stream()),
               "expert gate/up product")
         y = ctx.buffer("expert_rows", pairs, hidden, dtype="float32")
         check(self.lib.mb_expert_product(1, _ptr(act), ff, _ptr(down), _ptr(y), _ptr(plan), cap, top,
-                                         ff, hidden, _flag(x.dtype), bm, self._stream()),
+                                         ff, hidden, _flag(x.dtype), bm, None, self._stream()),
               "expert down product")
-        check(self.lib.mb_expert_combine(_ptr(y), _ptr(weights), _ptr(out), tokens, top, hidden,
+        check(self.lib.mb_expert_combine(_ptr(y), None if on_input else _ptr(weights), _ptr(out),
+                                         tokens, top, hidden,
                                          self._stream()), "expert_combine")
         self.launches += 4
 
-    def _expert_library(self, x, weights, gate_up, down, out, ctx, plan, cap, tokens, top):
+    def _expert_library(self, x, weights, gate_up, down, out, ctx, plan, cap, tokens, top,
+                        weight_on="output"):
         """Many pairs in bfloat16: the two grouped products are the library's (where the
         engine's other many-token products are the library's too), between this package's
         gather, gate and weighted sum. The rows lie in the plan's order throughout."""
@@ -1035,13 +1168,16 @@ class CudaOps:
         ends = flat[1 + 3 * cap + pairs:1 + 3 * cap + pairs + experts]
         place = flat[1 + 3 * cap + pairs + experts:]
         rows = ctx.buffer("expert_in", pairs, hidden)
+        on_input = weight_on == "input"
         check(self.lib.mb_expert_gather(_ptr(x), _ptr(perm), _ptr(rows), pairs, top, hidden,
-                                        self._stream()), "expert_gather")
+                                        _ptr(weights) if on_input else None, self._stream()),
+              "expert_gather")
         both = self._grouped_mm(rows, gate_up.transpose(1, 2), offs=ends)
         act = ctx.buffer("expert_act", pairs, ff)
         self.swiglu(both, act)
         y = self._grouped_mm(act, down.transpose(1, 2), offs=ends)
-        check(self.lib.mb_expert_combine_sorted(_ptr(y), _ptr(place), _ptr(weights), _ptr(out), tokens,
+        check(self.lib.mb_expert_combine_sorted(_ptr(y), _ptr(place),
+                                                None if on_input else _ptr(weights), _ptr(out), tokens,
                                                 top, hidden, self._stream()), "expert_combine")
         self.launches += 3
         self.library_calls += 2

@@ -86,8 +86,15 @@ class Model:
                     self.state_needs[(index, m)] = need
             for extra, part in enumerate(self._state_parts(self.blocks[call.block])):
                 self.state_needs[(index, len(mixers) + extra)] = part.state_need()
-        # a block that keeps state outside its mixers has to see every token as well
-        self.keeps_block_state = any(self._state_parts(block) for block in self.blocks)
+        # an embedding may keep per-request state too (the token in front of a step's first)
+        need = getattr(self.embedding, "state_need", lambda: None)()
+        if need is not None:
+            self.state_needs[self.EMBEDDING_STATE] = need
+        # a block (or an embedding) that keeps state outside the mixers has to see every token
+        self.keeps_block_state = need is not None or any(
+            self._state_parts(block) for block in self.blocks)
+
+    EMBEDDING_STATE = (-1, 0)       # the key of the embedding's state among `state_needs`
 
     @staticmethod
     def _state_parts(block) -> list:
@@ -134,7 +141,10 @@ class Model:
         None when no row is wanted. `kv_layers[c]` is (K pages, V pages) of cache layer c;
         `states[(i, m)]` the state tensor of mixer m of schedule entry i."""
         batch = ctx.batch
-        h = self.embedding.forward(batch.token_ids, ctx)
+        if self.EMBEDDING_STATE in self.state_needs:
+            h = self.embedding.forward(batch.token_ids, ctx, state=states[self.EMBEDDING_STATE])
+        else:
+            h = self.embedding.forward(batch.token_ids, ctx)
         delta = None
         schedule = self.spec.schedule
         for index, call in enumerate(schedule):

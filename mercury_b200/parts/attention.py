@@ -511,6 +511,152 @@ class SigmoidAttention(Mixer):
         return out
 
 
+class MaskedAttention(Mixer):
+    """Grouped-query softmax attention whose mask, cap, sink and number of maps are parameters.
+
+    Per token: q = Wq h, k = Wk h and v = Wv h (heads x dim, kv_heads x dim, kv_heads x value_dim),
+    each with a bias when `bias` names it ("q", "k", "v", "o"; a bias is `name + bias_suffix`); with
+    `values_from_keys` there is no Wv and the values are the keys as projected, before norm and
+    rotation. `qk_norm` "projection": q over all its heads' rows at once is divided by its root
+    mean square and multiplied by a weight of that many numbers, and so is k (before the
+    rotation). The position encoding turns q and k. `mask` = {"kind", "size", "keep_first"}: key j
+    is seen from position p iff j <= p and, for "sliding", p - j < size or j < keep_first (first
+    tokens that stay visible at their true positions); for "chunked", floor(p / size) = floor(j /
+    size), chunks counted from position 0; for "full", nothing more. score = q . k * scale, then
+    softcap * tanh(score / softcap) when `softcap` > 0; softmax over the seen keys, with exp(sink_h)
+    in the denominator when `sink` (one learned number per query head, no key, no value).
+
+    `maps` = 2 is differential attention (Ye et al., "Differential Transformer"): q holds heads x
+    2 x dim rows and k kv_heads x 2 x dim, head by head as [map 1, map 2]; each map is rotated
+    and attends on its own over the same values, and with lambda = exp(lq1 . lk1) - exp(lq2 .
+    lk2) + diff (four learned vectors of `dim` numbers, one lambda for the layer) a head's output
+    is (a1 - lambda a2) divided by its root mean square over value_dim, times 1 - diff.
+
+    An output projection (with a bias when `bias` names "o") closes it.
+    """
+
+    capturable = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 scale: float, eps: float, prefix: str, mask: dict | None = None,
+                 value_dim: int | None = None, bias: tuple = (), values_from_keys: bool = False,
+                 qk_norm: str | None = None, softcap: float = 0.0, sink: bool = False, maps: int = 1,
+                 diff: float = 0.0, names: dict | None = None, bias_suffix: str = ".b",
+                 position_encoding: PartSpec | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads do not divide into {num_kv_heads} groups")
+        if maps not in (1, 2):
+            raise ValueError(f"{maps} maps per head are not built (1 or 2)")
+        if qk_norm not in (None, "projection"):
+            raise ValueError(f"qk_norm={qk_norm!r} is neither None nor 'projection'")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.maps = head_dim, int(maps)
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
+        self.values_from_keys = bool(values_from_keys)
+        if self.values_from_keys and self.value_dim != self.maps * head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        mask = dict(mask or {"kind": "full"})
+        self.mask_kind = mask.get("kind", "full")
+        if self.mask_kind not in ("full", "sliding", "chunked"):
+            raise ValueError(f"mask kind {self.mask_kind!r}")
+        self.mask_size = int(mask.get("size", 0)) if self.mask_kind != "full" else 0
+        self.keep_first = int(mask.get("keep_first", 0)) if self.mask_kind == "sliding" else 0
+        if self.mask_kind != "full" and self.mask_size <= 0:
+            raise ValueError("a sliding or chunked mask needs a positive size")
+        self.scale, self.eps, self.prefix = float(scale), float(eps), prefix
+        self.bias = tuple(bias)
+        self.qk_norm, self.softcap, self.has_sink = qk_norm, float(softcap), bool(sink)
+        self.diff = float(diff)
+        self.position = (build_part("position_encoding", position_encoding)
+                         if position_encoding is not None else None)
+        self.q_size = num_heads * self.maps * head_dim
+        self.k_size = num_kv_heads * self.maps * head_dim
+        self.v_size = 0 if self.values_from_keys else num_kv_heads * self.value_dim
+        self.names = {"q": "q", "k": "k", "v": "v", "q_norm": "q.norm", "k_norm": "k.norm",
+                      "sink": "sink", "o": "o", "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
+        self.names.update(names or {})
+        self.bias_suffix = bias_suffix
+        self.lam = 0.0
+
+    def cache_need(self):
+        # a chunk never reaches further back than its size, so the pages behind that go back
+        # to the pool as they do behind a window
+        return CacheNeed(self.num_kv_heads, self.maps * self.head_dim, self.mask_size, self.value_dim,
+                         keep_first=self.keep_first)
+
+    def _projections(self):
+        return ("q", "k") if self.values_from_keys else ("q", "k", "v")
+
+    def tensor_specs(self):
+        p, n, b, h = self.prefix, self.names, self.bias_suffix, self.hidden_size
+        rows = {"q": self.q_size, "k": self.k_size, "v": self.v_size}
+        specs = []
+        for key in self._projections():
+            specs.append(TensorSpec(p + n[key], (rows[key], h), std=0.05))
+            if key in self.bias:
+                specs.append(TensorSpec(p + n[key] + b, (rows[key],), std=0.1))
+        if self.qk_norm:
+            specs += [TensorSpec(p + n["q_norm"], (self.q_size,), init="ones_normal", std=0.1),
+                      TensorSpec(p + n["k_norm"], (self.k_size,), init="ones_normal", std=0.1)]
+        if self.has_sink:
+            specs.append(TensorSpec(p + n["sink"], (self.num_heads,), std=1.0))
+        if self.maps == 2:
+            specs += [TensorSpec(p + n[key], (self.head_dim,), std=0.1)
+                      for key in ("lq1", "lk1", "lq2", "lk2")]
+        specs.append(TensorSpec(p + n["o"], (h, self.num_heads * self.value_dim)))
+        if "o" in self.bias:
+            specs.append(TensorSpec(p + n["o"] + b, (h,), std=0.1))
+        return specs + (self.position.tensor_specs() if self.position is not None else [])
+
+    def load(self, tensors, setup):
+        p, n, b = self.prefix, self.names, self.bias_suffix
+        keys = self._projections()
+        mats = [setup.place(tensors[p + n[key]]) for key in keys]
+        widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()
+        self.in_bias = None
+        if any(key in self.bias for key in keys):
+            pieces = [setup.place(tensors[p + n[key] + b]).to(widest) if key in self.bias
+                      else torch.zeros(mat.shape[0], dtype=widest, device=mat.device)
+                      for key, mat in zip(keys, mats)]
+            self.in_bias = torch.cat(pieces).contiguous()
+        # norms, sinks and lambda are float32 arithmetic: they are held so
+        self.q_norm = self.k_norm = self.sink = None
+        if self.qk_norm:
+            self.q_norm = setup.place(tensors[p + n["q_norm"]]).float().contiguous()
+            self.k_norm = setup.place(tensors[p + n["k_norm"]]).float().contiguous()
+        if self.has_sink:
+            self.sink = setup.place(tensors[p + n["sink"]]).float().contiguous()
+        if self.maps == 2:
+            lq1, lk1, lq2, lk2 = (tensors[p + n[key]].float() for key in ("lq1", "lk1", "lq2", "lk2"))
+            self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum())) + self.diff
+        self.out_weight = setup.place(tensors[p + n["o"]])
+        self.out_bias = setup.place(tensors[p + n["o"] + b]) if "o" in self.bias else None
+        if self.position is not None:
+            self.position.load(tensors, setup)
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops = x.shape[0], ctx.ops
+        pre = ctx.buffer("attn_in", tokens, self.in_weight.shape[0], dtype="float32")
+        ops.linear(x, self.in_weight, self.in_bias, pre)
+        tables = self.position.rotary_tables() if self.position is not None else None
+        pairing = getattr(self.position, "pairing", "halves")
+        layout = (self.num_heads, self.num_kv_heads, self.maps, self.head_dim, self.value_dim)
+        q = ctx.buffer("attn_q", tokens, self.q_size)
+        # the norms over the projections, the rotation, and the store of keys and values
+        ops.masked_prepare(pre, layout, self.q_norm, self.k_norm, self.eps, tables, pairing,
+                           ctx.batch, cache, q, self.values_from_keys)
+        attended = ctx.buffer("attended_v", tokens, self.num_heads * self.value_dim)
+        ops.masked_attention(q, layout, ctx.batch, cache, self.scale,
+                             (self.mask_kind, self.mask_size, self.keep_first), attended,
+                             softcap=self.softcap, sinks=self.sink, lam=self.lam, sub_eps=self.eps,
+                             out_scale=1.0 - self.diff if self.maps == 2 else 1.0)
+        out = ctx.sublayer_out(tokens, self.hidden_size)
+        ops.linear(attended, self.out_weight, self.out_bias, out)
+        return out
+
+
 register_mixer("mixed_head_attention", MixedHeadAttention)
 register_mixer("latent_attention", LatentAttention)
 register_mixer("sigmoid_attention", SigmoidAttention)
+register_mixer("masked_attention", MaskedAttention)

@@ -47,16 +47,52 @@ class PreNormBlock:
         return ff.forward(x, ctx)
 
 
+class NormedJoin(Part):
+    """How two mixers side by side become one sublayer output: each output is RMS-normed over
+    the model width with a plain weight of its own (`weight_names`), and the two are added
+    under `scales`."""
+
+    capturable = True
+
+    def __init__(self, size: int, eps: float, weight_names: tuple, scales: tuple = (0.5, 0.5)):
+        self.size, self.eps = int(size), float(eps)
+        self.weight_names, self.scales = tuple(weight_names), tuple(float(v) for v in scales)
+        if len(self.weight_names) != 2 or len(self.scales) != 2:
+            raise ValueError("a join takes two outputs")
+        self.weights = None
+
+    def tensor_specs(self):
+        return [TensorSpec(name, (self.size,), init="ones_normal", std=0.05)
+                for name in self.weight_names]
+
+    def load(self, tensors, setup):
+        # norms are float32 arithmetic
+        self.weights = [setup.place(tensors[name]).float().contiguous() for name in self.weight_names]
+
+
 class SandwichBlock:
     """A norm before AND behind each sublayer: h <- h + post(mixer(pre(h))), then, where the
     block has a feed-forward, h <- h + post'(ff(pre'(h))). The sums are made by the norm
     behind the sublayer (`normed_add`), which also computes the norm that comes next, so
-    the block leaves no pending delta."""
+    the block leaves no pending delta. With `mixers` (two) and `mixer_join` (a `NormedJoin`)
+    the mixer sublayer is two mixers side by side on the same normed input, joined before
+    the norm behind the sublayer. A feed-forward may return two tensors (routed experts and
+    a shared expert); their sum is what the norm behind it takes."""
 
-    def __init__(self, mixer: PartSpec, mixer_norm: PartSpec, mixer_post_norm: PartSpec,
+    def __init__(self, mixer_norm: PartSpec, mixer_post_norm: PartSpec, mixer: PartSpec | None = None,
                  feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None,
-                 feed_forward_post_norm: PartSpec | None = None):
-        self.mixer = build_part("mixer", mixer)
+                 feed_forward_post_norm: PartSpec | None = None, mixers: list | None = None,
+                 mixer_join: dict | None = None):
+        if (mixer is None) == (mixers is None):
+            raise ValueError("a block takes `mixer` or `mixers`")
+        self.side_mixers = None
+        self.join = None
+        if mixers is not None:
+            if len(mixers) != 2 or mixer_join is None:
+                raise ValueError("mixers side by side come as two, with a `mixer_join`")
+            self.side_mixers = [build_part("mixer", m) for m in mixers]
+            self.join = NormedJoin(**mixer_join)
+        self.mixer = build_part("mixer", mixer) if mixer is not None else None
         self.mixer_norm = build_part("norm", mixer_norm)
         self.mixer_post_norm = build_part("norm", mixer_post_norm)
         self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
@@ -68,10 +104,12 @@ class SandwichBlock:
             self.feed_forward_post_norm = build_part("norm", feed_forward_post_norm)
 
     def mixers(self):
-        return [self.mixer]
+        return list(self.side_mixers) if self.side_mixers is not None else [self.mixer]
 
     def parts(self):
-        out = [self.mixer_norm, self.mixer, self.mixer_post_norm]
+        out = [self.mixer_norm, *self.mixers(), self.mixer_post_norm]
+        if self.join is not None:
+            out.append(self.join)
         if self.feed_forward is not None:
             out += [self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm]
         return out
@@ -79,16 +117,31 @@ class SandwichBlock:
     def first_norm(self):
         return self.mixer_norm
 
+    def _mix(self, h, x, ctx, caches, states, then_norm):
+        if self.side_mixers is None:
+            mixed = self.mixer.forward(x, ctx, caches[0], states[0])
+            self.mixer_post_norm.normed_add(h, mixed, ctx, then_norm=then_norm)
+            return
+        outs = []
+        for index, mixer in enumerate(self.side_mixers):
+            ctx.side = index          # mixers side by side leave their outputs in buffers of their own
+            outs.append(mixer.forward(x, ctx, caches[index], states[index]))
+        ctx.side = 0
+        self.mixer_post_norm.joined_add(h, outs[0], outs[1], ctx, then_norm=then_norm,
+                                        norm_weights=self.join.weights, scales=self.join.scales)
+
     def forward(self, h, delta, ctx, caches, states, next_norm=None):
         x = self.mixer_norm.add_norm(h, delta, ctx)
-        mixed = self.mixer.forward(x, ctx, caches[0], states[0])
         if self.feed_forward is None:
-            self.mixer_post_norm.normed_add(h, mixed, ctx, then_norm=next_norm)
+            self._mix(h, x, ctx, caches, states, next_norm)
             return None
-        self.mixer_post_norm.normed_add(h, mixed, ctx, then_norm=self.feed_forward_norm)
+        self._mix(h, x, ctx, caches, states, self.feed_forward_norm)
         x = self.feed_forward_norm.add_norm(h, None, ctx)
-        self.feed_forward_post_norm.normed_add(h, self.feed_forward.forward(x, ctx), ctx,
-                                               then_norm=next_norm)
+        out = self.feed_forward.forward(x, ctx)
+        if isinstance(out, tuple):
+            self.feed_forward_post_norm.joined_add(h, out[0], out[1], ctx, then_norm=next_norm)
+        else:
+            self.feed_forward_post_norm.normed_add(h, out, ctx, then_norm=next_norm)
         return None
 
 

@@ -13,7 +13,9 @@ another registered kind, not a change to the generic model.
 
 from __future__ import annotations
 
-from .base import Embedding, Head, TensorSpec, register_embedding, register_head
+import torch
+
+from .base import Embedding, Head, StateNeed, TensorSpec, register_embedding, register_head
 
 
 class TokenEmbedding(Embedding):
@@ -68,6 +70,40 @@ class PositionedEmbedding(TokenEmbedding):
         return h
 
 
+class BigramEmbedding(TokenEmbedding):
+    """Token row plus a row of a hashed table of token pairs: stream[t] = table[token[t]] +
+    pairs[(token[t-1] * mul_prev + token[t] * mul_cur) mod buckets], and for a sequence's
+    first token the row behind the buckets (the table has buckets + 1 rows). The token in
+    front of a step's first token is per-request state (`state_need()`): one int32 per slot,
+    which the lookup kernel reads and brings up to date."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, pair_name: str,
+                 buckets: int, mul_prev: int, mul_cur: int):
+        super().__init__(vocab_size, hidden_size, weight_name)
+        self.pair_name = pair_name
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.pair_table = None
+
+    def state_need(self):
+        return StateNeed((1,), torch.int32)
+
+    def tensor_specs(self):
+        return super().tensor_specs() + [
+            TensorSpec(self.pair_name, (self.buckets + 1, self.hidden_size))]
+
+    def load(self, tensors, setup):
+        super().load(tensors, setup)
+        self.pair_table = setup.place_named(tensors, self.pair_name)
+
+    def forward(self, token_ids, ctx, state=None):
+        if state is None:
+            raise ValueError("the bigram embedding needs its state: every sequence's last token")
+        h = ctx.buffer("residual", token_ids.shape[0], self.hidden_size, dtype="float32")
+        ctx.ops.embed_bigram(token_ids, self.table, self.pair_table, self.buckets, self.mul_prev,
+                             self.mul_cur, state, ctx.batch, h)
+        return h
+
+
 class LinearHead(Head):
     capturable = True
 
@@ -105,5 +141,6 @@ class SoftCappedHead(LinearHead):
 
 register_embedding("lookup", TokenEmbedding)
 register_embedding("lookup_learned_positions", PositionedEmbedding)
+register_embedding("lookup_bigram", BigramEmbedding)
 register_head("linear", LinearHead)
 register_head("linear_softcap", SoftCappedHead)

@@ -9,6 +9,8 @@ itself is float32, so nothing is rounded between layers.
 
 from __future__ import annotations
 
+import torch
+
 from .base import Norm, TensorSpec, register_norm
 
 # A norm may also stand BEHIND a sublayer (`RMSNorm.normed_add`): the sublayer's output is
@@ -112,6 +114,31 @@ class RMSNorm(Norm):
                             follow.weight if follow is not None else None,
                             follow.eps if follow is not None else 0.0, out, **extra)
         ctx.prenormed = (follow, Computed(out)) if follow is not None else None
+
+    def joined_add(self, h, first, second, ctx, then_norm=None, norm_weights=None,
+                   scales=(1.0, 1.0)):
+        """h <- h + norm(a n(first) + b n(second)) with (a, b) = `scales`: two outputs that ran side
+        by side, joined, then this norm, then the sum into the stream. `norm_weights` = [w1, w2]
+        (float32): each output first passes an RMS norm of its own with that weight (this
+        norm's eps), n(x) = rmsnorm(x) * w; without them n(x) = x. With `then_norm` the same
+        kernel leaves that norm's output of the new stream in `ctx.prenormed`."""
+        follow = then_norm if (isinstance(then_norm, RMSNorm) and then_norm.size == self.size) else None
+        out = ctx.buffer("normed", h.shape[0], self.size) if follow is not None else None
+        wx, wy = norm_weights if norm_weights is not None else (None, None)
+        ctx.ops.rmsnorm_join_add(h, first, second, wx, wy, scales[0], scales[1],
+                                 self._float_weight(), self.eps,
+                                 follow._float_weight() if follow is not None else None,
+                                 follow.eps if follow is not None else 0.0, out)
+        ctx.prenormed = (follow, Computed(out)) if follow is not None else None
+
+    def _float_weight(self):
+        """The weight in float32 (made once; the weight itself where it is float32 already)."""
+        if self.weight.dtype == torch.float32:
+            return self.weight
+        held = getattr(self, "_weight_f32", None)
+        if held is None:
+            held = self._weight_f32 = self.weight.float().contiguous()
+        return held
 
     def add_norm(self, h, delta, ctx, rows=None, defer=False):
         """`defer=True` says that the consumer takes a `PendingNorm`; one is returned when

@@ -34,13 +34,18 @@ request: [S | inputs one token back | two tokens back | ...].
            key u = k / sqrt(sum k^2 + unit_eps) of each head, S_t = diag(w) S_(t-1) - (a * u)
            (u^T S_(t-1)) + k v^T, both terms reading the matrix as the token found it; o = S_t^T
            r; out = Wo (o / rms(o) per head * w_norm * sigmoid(Wg h)). Its state is S alone.
+`Retention` (Sun et al., "Retentive Network: A Successor to Transformer for Large Language
+           Models"): q = Wq h, k = Wk h (heads x dim), v = Wv h (heads x vdim); q and k turned by
+           the position encoding, k then times key_scale (dim^-1/2); per head S_t = decay_h
+           S_(t-1) + k_t v_t^T with a fixed decay per head, o_t = S_t^T q_t, neither softmax nor
+           denominator; out = Wo (o / rms(o) per head * silu(Wg h)). Its state is S alone.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .base import Mixer, StateNeed, TensorSpec, register_mixer
+from .base import Mixer, PartSpec, StateNeed, TensorSpec, build_part, register_mixer
 
 
 class MinGRU(Mixer):
@@ -375,7 +380,74 @@ class GeneralizedDeltaRule(Mixer):
         return out
 
 
+class Retention(Mixer):
+    capturable = True
+
+    def __init__(self, hidden_size: int, heads: int, key_dim: int, value_dim: int, decay: list,
+                 eps: float, prefix: str, key_scale: float | None = None, names: dict | None = None,
+                 position_encoding: PartSpec | None = None):
+        """`decay`: one number per head; `key_scale`: what the rotated keys are multiplied by
+        (default key_dim^-1/2)."""
+        if len(decay) != heads:
+            raise ValueError(f"{len(decay)} decays for {heads} heads")
+        self.hidden_size, self.heads, self.key_dim, self.value_dim = hidden_size, heads, key_dim, value_dim
+        self.decay_values = [float(v) for v in decay]
+        self.eps, self.prefix = float(eps), prefix
+        self.key_scale = float(key_dim) ** -0.5 if key_scale is None else float(key_scale)
+        self.position = (build_part("position_encoding", position_encoding)
+                         if position_encoding is not None else None)
+        self.keys, self.inner = heads * key_dim, heads * value_dim
+        # what one product reads off the layer's input: [q | k | v | g]
+        self.offsets = {"q": 0, "k": self.keys, "v": 2 * self.keys, "g": 2 * self.keys + self.inner}
+        self.proj = 2 * self.keys + 2 * self.inner
+        self.cells = heads * key_dim * value_dim
+        self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+        self.names.update(names or {})
+
+    def state_need(self):
+        return StateNeed((self.cells,), torch.float32)
+
+    def tensor_specs(self):
+        p, n, h = self.prefix, self.names, self.hidden_size
+        return [TensorSpec(p + n["q"], (self.keys, h), std=0.05),
+                TensorSpec(p + n["k"], (self.keys, h), std=0.05),
+                TensorSpec(p + n["v"], (self.inner, h), std=0.05),
+                TensorSpec(p + n["g"], (self.inner, h), std=0.05),
+                TensorSpec(p + n["o"], (h, self.inner))] + (
+                    self.position.tensor_specs() if self.position is not None else [])
+
+    def load(self, tensors, setup):
+        p, n = self.prefix, self.names
+        mats = [setup.place(tensors[p + n[key]]) for key in ("q", "k", "v", "g")]
+        widest = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.in_weight = torch.cat([t.to(widest) for t in mats], dim=0).contiguous()
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=setup.device)
+        # the read-out's norm has no weight: the kernel that norms and gates takes ones
+        self.norm_weight = torch.ones(self.value_dim, dtype=torch.float32, device=setup.device)
+        self.out_weight = setup.place(tensors[p + n["o"]])
+        if self.position is not None:
+            self.position.load(tensors, setup)
+
+    def forward(self, x, ctx, cache, state):
+        tokens, ops, at = x.shape[0], ctx.ops, self.offsets
+        # float32: what enters the recurrence is 32-bit
+        pre = ctx.buffer("recurrent_in", tokens, self.proj, dtype="float32")
+        ops.linear(x, self.in_weight, None, pre)
+        tables = self.position.rotary_tables() if self.position is not None else None
+        pairing = getattr(self.position, "pairing", "halves")
+        o = ctx.buffer("recurrent_y", tokens, self.inner, dtype="float32")
+        ops.retention_scan(pre, (at["q"], at["k"], at["v"]), self.decay, self.key_scale,
+                           (self.heads, self.key_dim, self.value_dim), tables, pairing, state,
+                           ctx.batch, o)
+        mixed = ctx.buffer("recurrent_mixed", tokens, self.inner)
+        ops.gated_group_norm(o, pre, at["g"], self.norm_weight, self.heads, self.eps, False, mixed)
+        out = ctx.sublayer_out(tokens, self.hidden_size)
+        ops.linear(mixed, self.out_weight, None, out)
+        return out
+
+
 register_mixer("mingru", MinGRU)
+register_mixer("retention", Retention)
 register_mixer("generalized_delta_rule", GeneralizedDeltaRule)
 register_mixer("mamba2", Mamba2)
 register_mixer("gated_delta_rule", GatedDeltaRule)

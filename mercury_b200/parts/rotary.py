@@ -10,6 +10,11 @@ feature i + rotary_dim/2; "interleaved" pairs feature 2i with feature 2i + 1 (th
 theta^(-2i/rotary_dim)). The tables are the same for both; the rotate-and-store kernels of
 the grouped-query attention know the halves only, so an interleaved encoding answers
 `fused_form()` with None and serves the mixers that ask for `pairing` themselves.
+
+`scaling` = {"factor", "low", "high", "original"} slows the long wavelengths down (the
+frequency scaling that Llama 3.1 uses): with the wavelength l = 2 pi / f, a frequency with l < original / high is kept, one with l > original /
+low becomes f / factor, and between the two it is (1 - s) f / factor + s f with s = (original
+/ l - low) / (high - low).
 """
 
 from __future__ import annotations
@@ -23,12 +28,18 @@ class RotaryEncoding(PositionEncoding):
     capturable = True
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None,
-                 table_precision: str = "float32", pairing: str = "halves"):
+                 table_precision: str = "float32", pairing: str = "halves",
+                 scaling: dict | None = None):
         """`table_precision` "float64": angles, cosines and sines are computed in 64-bit and
         rounded once to the float32 tables."""
         if pairing not in ("halves", "interleaved"):
             raise ValueError(f"pairing={pairing!r} is neither 'halves' nor 'interleaved'")
         self.pairing = pairing
+        self.scaling = None
+        if scaling:
+            self.scaling = tuple(float(scaling[key]) for key in ("factor", "low", "high", "original"))
+            if min(self.scaling) <= 0 or self.scaling[1] == self.scaling[2]:
+                raise ValueError(f"rotary scaling {scaling!r}: positive numbers, low != high")
         self.table_precision = table_precision
         self.head_dim = head_dim
         self.theta = float(theta)
@@ -43,6 +54,13 @@ class RotaryEncoding(PositionEncoding):
             real = torch.float64 if self.table_precision == "float64" else torch.float32
             exponent = torch.arange(0, self.rotary_dim, 2, dtype=real) / self.rotary_dim
             inv_freq = 1.0 / (self.theta ** exponent)
+            if self.scaling is not None:
+                factor, low, high, original = self.scaling
+                wave = 2.0 * torch.pi / inv_freq
+                blend = ((original / wave - low) / (high - low)).clamp(0.0, 1.0)
+                mixed = (1.0 - blend) * inv_freq / factor + blend * inv_freq
+                inv_freq = torch.where(wave < original / high, inv_freq,
+                                       torch.where(wave > original / low, inv_freq / factor, mixed))
             positions = torch.arange(setup.max_positions, dtype=real)
             angles = torch.outer(positions, inv_freq)
             return (angles.cos().float().to(setup.device).contiguous(),
@@ -51,7 +69,7 @@ class RotaryEncoding(PositionEncoding):
         # every layer with the same constants reads the same pair of tables
         self.cos, self.sin = setup.derived(
             ("rotary", self.rotary_dim, self.theta, setup.max_positions, str(setup.device),
-             self.table_precision), tables)
+             self.table_precision, self.scaling), tables)
 
     def fused_form(self):
         return "rotary" if self.pairing == "halves" else None

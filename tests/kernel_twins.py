@@ -89,7 +89,7 @@ class TorchOps:
         self.linear(x, weight, None, gate_up)
         self.swiglu(gate_up, out)
 
-    def linear_gated(self, x, weight, out, ctx, activation):
+    def linear_gated(self, x, weight, out, ctx, activation, limit=0.0, slope=1.0):
         x = self._x(x)
         width = out.shape[-1]
         both = x.to(self.acc) @ weight.to(self.acc).T
@@ -99,6 +99,10 @@ class TorchOps:
             act = gate * torch.sigmoid(gate)
         elif activation == "gelu_tanh":
             act = 0.5 * gate * (1.0 + torch.tanh(0.7978845608028654 * (gate + 0.044715 * gate ** 3)))
+        elif activation == "clamped_sigmoid":
+            gate = gate.clamp(max=limit)
+            act = gate * torch.sigmoid(slope * gate)
+            up = up.clamp(-limit, limit) + 1.0
         else:
             raise ValueError(activation)
         out.copy_((act * up).to(out.dtype))
@@ -609,6 +613,140 @@ class TorchOps:
             o = torch.einsum("hqk,hkd->qhd", weights, vals)
             out[begin:end] = o.reshape(q_len, heads * vdim).to(out.dtype)
 
+    # ---------------------------------------------------------------- masked attention
+
+    def embed_bigram(self, token_ids, table, pairs, buckets, mul_prev, mul_cur, state, batch, out):
+        ids = token_ids.long()
+        rows = table[ids].to(self.acc)
+        starts, slots = batch.q_start.tolist(), batch.slots.tolist()
+        positions = batch.positions.tolist()
+        pair_rows = torch.zeros_like(rows)
+        live = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
+        for s in range(batch.num_seqs):
+            begin, end = starts[s], starts[s + 1]
+            if end <= begin:
+                continue
+            prev = int(state[slots[s], 0])
+            for t in range(begin, end):
+                tok = int(ids[t])
+                row = buckets if positions[t] == 0 else (prev * mul_prev + tok * mul_cur) % buckets
+                pair_rows[t] = pairs[row].to(self.acc)
+                live[t] = True
+                prev = tok
+            state[slots[s], 0] = prev
+        out.copy_(((rows + pair_rows) * live[:, None]).to(out.dtype))
+
+    def rmsnorm_join_add(self, h, x, y, wx, wy, a, b, weight, eps, next_weight, next_eps, out):
+        def unit(v):
+            return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+
+        xv, yv = x.to(self.acc), y.to(self.acc)
+        if wx is not None:
+            xv = unit(xv) * wx.to(self.acc)
+        if wy is not None:
+            yv = unit(yv) * wy.to(self.acc)
+        z = a * xv + b * yv
+        h.add_((unit(z) * weight.to(self.acc)).to(h.dtype))
+        if next_weight is not None:
+            v = h.to(self.acc)
+            out.copy_((v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + next_eps)
+                       * next_weight.to(self.acc)).to(out.dtype))
+
+    def masked_prepare(self, pre, layout, q_norm, k_norm, eps, tables, pairing, batch, cache, q,
+                       values_from_keys):
+        heads, kv_heads, maps, dim, vdim = layout
+        tokens = pre.shape[0]
+        pos = batch.positions[:tokens].long()
+        qs, ks = heads * maps * dim, kv_heads * maps * dim
+        qx = pre[:, :qs].to(self.acc)
+        kx = pre[:, qs:qs + ks].to(self.acc)
+        vx = (kx if values_from_keys else pre[:, qs + ks:].to(self.acc)).view(tokens, kv_heads, vdim)
+        kn = kx
+        if q_norm is not None:
+            qx = qx * torch.rsqrt(qx.pow(2).mean(-1, keepdim=True) + eps) * q_norm.to(self.acc)
+            kn = kx * torch.rsqrt(kx.pow(2).mean(-1, keepdim=True) + eps) * k_norm.to(self.acc)
+        qx, kn = qx.view(tokens, heads * maps, dim), kn.view(tokens, kv_heads * maps, dim)
+        if tables is not None:
+            rot = 2 * tables[0].shape[1]
+            qx = torch.cat([self._rotate(qx[..., :rot], pos, tables, pairing), qx[..., rot:]], dim=-1)
+            kn = torch.cat([self._rotate(kn[..., :rot], pos, tables, pairing), kn[..., rot:]], dim=-1)
+        q.copy_(qx.reshape(tokens, qs).to(q.dtype))
+        keep, page, offset = self._page_slots(batch, cache, tokens)
+        cache.k[page[keep], :, offset[keep], :] = kn.reshape(tokens, kv_heads, maps * dim)[keep].to(cache.k.dtype)
+        cache.v[page[keep], :, offset[keep], :] = vx[keep].to(cache.v.dtype)
+
+    def masked_attention(self, q, layout, batch, cache, scale, mask, out, softcap=0.0, sinks=None,
+                         lam=0.0, sub_eps=0.0, out_scale=1.0):
+        heads, kv_heads, maps, dim, vdim = layout
+        kind, size, keep_first = mask
+        group = heads // kv_heads
+        q_start, kv_lens = batch.q_start.tolist(), batch.kv_len.tolist()
+        ps = cache.page_size
+        for s in range(batch.num_seqs):
+            begin, end = q_start[s], q_start[s + 1]
+            q_len, kv_len = end - begin, kv_lens[s]
+            if q_len == 0:
+                continue
+            key_pos = torch.arange(kv_len, device=q.device)[None, :]
+            q_pos = torch.arange(kv_len - q_len, kv_len, device=q.device)[:, None]
+            seen = key_pos <= q_pos
+            if kind == "sliding":
+                seen = seen & ((q_pos - key_pos < size) | (key_pos < keep_first))
+            elif kind == "chunked":
+                seen = seen & (q_pos // size == key_pos // size)
+            pages = cache.table[s, :-(-kv_len // ps)].long()
+            wanted = seen.any(0)
+            if bool((wanted & ~(pages[key_pos[0] // ps] >= 0)).any()):
+                raise AssertionError("a visible key's page was given back")
+            pages = pages.clamp(min=0)
+            keys = cache.k[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, maps, dim)[:, :kv_len]
+            vals = cache.v[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, vdim)[:, :kv_len]
+            keys = torch.where(wanted[None, :, None, None], keys.to(self.acc), torch.zeros((), dtype=self.acc))
+            vals = torch.where(wanted[None, :, None], vals.to(self.acc), torch.zeros((), dtype=self.acc))
+            keys = keys.repeat_interleave(group, dim=0)
+            vals = vals.repeat_interleave(group, dim=0)
+            qs = q[begin:end].view(q_len, heads, maps, dim).to(self.acc)
+            result = None
+            for mp in range(maps):
+                scores = torch.einsum("qhd,hkd->hqk", qs[:, :, mp], keys[:, :, mp]) * scale
+                if softcap > 0:
+                    scores = softcap * torch.tanh(scores / softcap)
+                scores = scores.masked_fill(~seen[None], float("-inf"))
+                top = scores.max(-1, keepdim=True).values
+                if sinks is not None:
+                    top = torch.maximum(top, sinks.to(self.acc)[:, None, None])
+                e = torch.exp(scores - top)
+                den = e.sum(-1, keepdim=True)
+                if sinks is not None:
+                    den = den + torch.exp(sinks.to(self.acc)[:, None, None] - top)
+                a = torch.einsum("hqk,hkd->qhd", e / den, vals)
+                result = a if mp == 0 else result - lam * a
+            if maps == 2:
+                result = result * torch.rsqrt(result.pow(2).mean(-1, keepdim=True) + sub_eps) * out_scale
+            out[begin:end] = result.reshape(q_len, heads * vdim).to(out.dtype)
+
+    def retention_scan(self, pre, offsets, decay, key_scale, layout, tables, pairing, cells, batch, o):
+        heads, dim, vdim = layout
+        at_q, at_k, at_v = offsets
+        for begin, end, slot in self._sequences(batch):
+            count = end - begin
+            pos = batch.positions[begin:end].long()
+            qx = pre[begin:end, at_q:at_q + heads * dim].to(self.acc).view(count, heads, dim)
+            kx = pre[begin:end, at_k:at_k + heads * dim].to(self.acc).view(count, heads, dim)
+            vx = pre[begin:end, at_v:at_v + heads * vdim].to(self.acc).view(count, heads, vdim)
+            if tables is not None:
+                rot = 2 * tables[0].shape[1]
+                qx = torch.cat([self._rotate(qx[..., :rot], pos, tables, pairing), qx[..., rot:]], dim=-1)
+                kx = torch.cat([self._rotate(kx[..., :rot], pos, tables, pairing), kx[..., rot:]], dim=-1)
+            kx = kx * key_scale
+            # the matrices lie column by column: [head][vdim][dim]
+            s = cells[slot].view(heads, vdim, dim).to(self.acc).clone()
+            g = decay.to(self.acc)[:, None, None]
+            for t in range(count):
+                s = g * s + vx[t][:, :, None] * kx[t][:, None, :]
+                o[begin + t] = torch.einsum("hpd,hd->hp", s, qx[t]).reshape(-1).to(o.dtype)
+            cells[slot] = s.reshape(-1).to(cells.dtype)
+
     # ---------------------------------------------------------------- generalized delta rule
 
     def tanh_slice(self, pre, offset, count, out):
@@ -678,7 +816,8 @@ class TorchOps:
         chosen.copy_(index.to(chosen.dtype))
         weights.copy_((s.gather(1, index) * route_scale).to(weights.dtype))
 
-    def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx=None):
+    def expert_feed_forward(self, x, chosen, weights, gate_up, down, out, ctx=None,
+                            weight_on="output"):
         """out[t] = sum_j weights[t, j] * down[e] (silu(gate[e] x[t]) * (up[e] x[t])), e =
         chosen[t, j]; gate_up [experts, 2 ff, hidden] (gate rows first), down [experts,
         hidden, ff]."""
@@ -691,10 +830,12 @@ class TorchOps:
             if rows.numel() == 0:
                 continue
             both = (x[rows].to(self.acc) @ gate_up[e].to(self.acc).T)
+            w = (weights[rows].to(self.acc) * hit[rows]).sum(-1, keepdim=True)
+            if weight_on == "input":      # the weight on what the expert reads (no biases)
+                both = both * w
             act = (both[:, :ff] * torch.sigmoid(both[:, :ff]) * both[:, ff:]).to(x.dtype).to(self.acc)
             y = act @ down[e].to(self.acc).T
-            w = (weights[rows].to(self.acc) * hit[rows]).sum(-1, keepdim=True)
-            total[rows] += w * y
+            total[rows] += y if weight_on == "input" else w * y
         out.copy_(total.to(out.dtype))
 
     # ---------------------------------------------------------------- sampling
