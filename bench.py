@@ -887,6 +887,126 @@ def sisavik_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
     }
 
 
+LIZAZEN_SIZES = {
+    # width, query heads, key/value heads, head size, feed-forward, experts, experts a token
+    # uses, window / chunk, kept first tokens
+    "0.5b": (896, 14, 2, 64, 4864, 16, 4, 1024, 64),
+    "1.5b": (1536, 12, 2, 128, 8960, 16, 4, 1024, 64),
+}
+
+
+def lizazen_config(size: str) -> dict:
+    """A Lizazen model at the layer sizes of `size`: capped window attention with a dense
+    feed-forward, differential attention (two maps of 64 over values of 128) with routed
+    experts and a shared expert (active width: the dense feed-forward's), differential
+    attention with a dense feed-forward, and chunked attention beside retention with routed
+    experts, twice over."""
+    width, heads, kv_heads, dim, ff, experts, top, window, keep = LIZAZEN_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": ff // (top + 1)}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": ff // (top + 1)}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    capped = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+              "softcap": 50.0, "mask": {"size": window},
+              "rot": {"base": 500000.0, "dims": dim,
+                      "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    maps = width // 128
+    differential = {"heads": maps, "kv_heads": max(1, maps // 7) if maps % 7 == 0 else 2, "dim": 64,
+                    "vdim": 128, "diff": 0.6, "scale": 0.125,
+                    "mask": {"size": window, "keep_first": keep}, "rot": {"base": 10000.0, "dims": 32}}
+    parallel = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                         "scale": dim ** -0.5, "mask": {"size": window},
+                         "rot": {"base": 10000.0, "dims": dim // 2}},
+                "right": {"heads": width // 128, "dim": 64, "vdim": 128,
+                          "decay": [1.0 - 2.0 ** (-5 - i % 8) for i in range(width // 128)],
+                          "rot": {"base": 10000.0, "dims": 64}}}
+    layers = []
+    for _ in range(0, DESIGN_LAYERS, 4):
+        layers += [{"type": "attention", "mixer": capped, "mlp": dense},
+                   {"type": "attention_2", "mixer": differential, "mlp": moe},
+                   {"type": "attention_2", "mixer": differential, "mlp": dense},
+                   {"type": "parallel", "mixer": parallel, "mlp": moe}]
+    return {"architecture": "Lizazen", "width": width, "vocab": DESIGN_VOCAB,
+            "max_positions": MODEL_LEN, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7}},
+            "layers": layers[:DESIGN_LAYERS]}
+
+
+def chunk_pairs(tokens: int, chunk: int) -> int:
+    """(query, key) pairs of a prompt of `tokens` under chunks of `chunk` positions."""
+    return sum(p % chunk + 1 for p in range(tokens))
+
+
+def lizazen_costs(raw: dict, batch: int, context: int, tokens: int) -> dict:
+    """Per class of kernel call, what a Lizazen model has to read (decode step, bytes) or
+    compute (prompt step, flops; bytes for the classes that only move data)."""
+    w, v = raw["width"], raw["vocab"]
+    products = head = 2 * v * w
+    gated = att_bytes = att_flops = state_bytes = scan_flops = rec_tokens = rotary = 0
+    expert_bytes = expert_flops = router = 0
+    norms = 1
+
+    def attention(m, kind, maps=1, from_keys=False):
+        nonlocal products, att_bytes, att_flops, rotary
+        qk = (m["heads"] + m["kv_heads"]) * maps * m["dim"]
+        values = 0 if from_keys else m["kv_heads"] * m["vdim"]
+        products += 2 * ((qk + values) * w + m["heads"] * m["vdim"] * w)
+        size, keep = m["mask"]["size"], m["mask"].get("keep_first", 0)
+        reach = min(context + 1, size + keep) if kind == "sliding" else context % size + 1
+        att_bytes += batch * reach * 2 * m["kv_heads"] * (maps * m["dim"] + m["vdim"])
+        pairs = seen_pairs(tokens, 0, size, keep) if kind == "sliding" else chunk_pairs(tokens, size)
+        att_flops += m["heads"] * maps * 2 * (m["dim"] + m["vdim"]) * pairs
+        rotary += 4 * (qk + values) + 2 * (qk + m["kv_heads"] * m["vdim"])
+
+    for layer in raw["layers"]:
+        m = layer["mixer"]
+        norms += 2
+        if layer["type"] == "attention":
+            attention(m, "sliding", from_keys=True)
+        elif layer["type"] == "attention_2":
+            attention(m, "sliding", maps=2)
+        else:
+            attention(m["left"], "chunked")
+            right = m["right"]
+            keys, inner = right["heads"] * right["dim"], right["heads"] * right["vdim"]
+            products += 2 * ((2 * keys + 2 * inner) * w + inner * w)
+            state_bytes += 2 * 4 * right["heads"] * right["dim"] * right["vdim"]
+            scan_flops += 4 * right["heads"] * right["dim"] * right["vdim"]
+            rec_tokens += 4 * (2 * keys + 2 * inner) + 4 * inner + 2 * inner
+        mlp = layer["mlp"]
+        if mlp is None:
+            continue
+        norms += 2
+        if mlp["kind"] == "dense":
+            gated += 2 * 2 * mlp["ff"] * w
+            products += 2 * mlp["ff"] * w
+        else:
+            experts, top, ff = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            router += 4 * experts * w
+            per_expert = 2 * 3 * ff * w
+            expert_bytes += min(experts, batch * top) * per_expert
+            expert_flops += top * per_expert
+            if mlp.get("shared"):
+                gated += 2 * 2 * mlp["shared"]["ff"] * w
+                products += 2 * mlp["shared"]["ff"] * w
+    t = tokens
+    per_row = w * (4 + 2 + 4 + 2 + 4) // 2
+    return {
+        "decode": {"product": ("hbm", products), "gated product": ("hbm", gated),
+                   "attention": ("hbm", att_bytes), "expert products": ("hbm", expert_bytes),
+                   "router": ("hbm", router),
+                   "recurrence": ("hbm", batch * (state_bytes + rec_tokens)),
+                   "rotary + store": ("hbm", batch * rotary),
+                   "norm": ("hbm", norms * batch * per_row)},
+        "prefill": {"product": ("tensor", t * (products - head) + head),
+                    "gated product": ("tensor", t * gated),
+                    "attention": ("tensor", att_flops),
+                    "expert products": ("tensor", t * expert_flops),
+                    "recurrence": ("tensor", t * scan_flops),
+                    "rotary + store": ("hbm", t * rotary),
+                    "norm": ("hbm", norms * t * per_row)},
+    }
+
+
 def classes_of(torch, runner, batch, context, vocab, costs, peak) -> dict:
     """Milliseconds per class of kernel call of a decode step and of a prompt step (events
     around every call, the launches queued behind a delay on the device), with the fraction
@@ -951,7 +1071,9 @@ def run_designs(args) -> dict:
                   (("kinelix", kinelix_config(size)), ("fegenex", fegenex), ("qwen2", qwen2))
                   if args.design == "kinelix" else
                   (("sisavik", sisavik_config(size)), ("kinelix", kinelix_config(size)),
-                   ("qwen2", qwen2)))
+                   ("qwen2", qwen2)) if args.design == "sisavik" else
+                  (("lizazen", lizazen_config(size)), ("sisavik", sisavik_config(size)),
+                   ("kinelix", kinelix_config(size)), ("qwen2", qwen2)))
         for label, raw in models:
             _entry, config = config_from_dict(raw)
             tensors = random_tensors(config, SEED, torch.bfloat16)
@@ -965,6 +1087,7 @@ def run_designs(args) -> dict:
             costs = (design_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "fegenex"
                      else kinelix_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "kinelix"
                      else sisavik_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "sisavik"
+                     else lizazen_costs(raw, batch, CONTEXT, PREFILL_TOKENS) if label == "lizazen"
                      else class_costs(raw, batch, CONTEXT, PREFILL_TOKENS))
             row[label] = {"prefill_ms": round(prefill_ms, 3),
                           "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1),
@@ -1113,7 +1236,7 @@ def main() -> int:
                    help="run one part only (for profilers and side workloads); prints its own JSON")
     p.add_argument("--size", default=None, choices=tuple(SIZES),
                    help="layer sizes of --only decode/prefill/mixed (default 0.5b; mixed: 1.5b)")
-    p.add_argument("--design", default="fegenex", choices=("fegenex", "kinelix", "sisavik"),
+    p.add_argument("--design", default="fegenex", choices=("fegenex", "kinelix", "sisavik", "lizazen"),
                    help="which design --only designs measures beside the closest existing models")
     p.add_argument("--policy", default="lpm", choices=("fcfs", "lpm", "lpm_aging"))
     p.add_argument("--batch", type=int, default=BATCH, help="decode batch of --only decode")

@@ -155,6 +155,10 @@ _SIGNATURES = {
                             c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int,
                             c_float, c_float, c_float, c_int, c_int, c_void_p],
+    "mb_masked_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                                c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
     "mb_retention_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
                           c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_int, c_void_p],
@@ -236,6 +240,8 @@ def load():
     lib.mb_sigmoid_attention_mma_supports.restype = c_int
     lib.mb_sigmoid_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mb_sigmoid_attention_scratch_floats.restype = c_longlong
+    lib.mb_masked_attention_mma_supports.argtypes = [c_int, c_int, c_int]
+    lib.mb_masked_attention_mma_supports.restype = c_int
     lib.mb_masked_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.mb_masked_attention_scratch_floats.restype = c_longlong
     _LIB = lib

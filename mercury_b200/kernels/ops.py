@@ -969,27 +969,39 @@ class CudaOps:
         self._check_limits(cache)
         tokens = q.shape[0]
         group = heads // kv_heads
+        # prompt portions in bfloat16 with key and value sizes the tensor-core kernel takes run
+        # there (`kernel` forces "mma" or "simt"); everything else on the CUDA cores
+        mma_ok = (q.dtype == torch.bfloat16
+                  and bool(self.lib.mb_masked_attention_mma_supports(maps, dim, vdim)))
+        if kernel == "mma" and not mma_ok:
+            raise KernelError(f"the tensor-core masked attention takes bfloat16 with key and value "
+                              f"sizes of 64 or 128, not {q.dtype} with {maps} x {dim} and {vdim}")
+        use_mma = mma_ok and (kernel == "mma" or (kernel is None and batch.max_q_len * group >= 64))
+        rows, keys = (64, 64) if use_mma else (16, 32)
         if getattr(batch, "attention_splits", None):
             splits = batch.attention_splits
         else:
             reach = batch.max_kv_len if kind == "full" else min(
                 batch.max_kv_len, size + keep_first + batch.max_q_len)
-            tiles = -(-batch.max_q_len * group // 16)
+            tiles = -(-batch.max_q_len * group // rows)
             blocks = batch.num_seqs * tiles * kv_heads
-            key_tiles = -(-reach // 32)
+            key_tiles = -(-reach // keys)
             splits = 1
             if blocks < self.sm_count and key_tiles >= 4:
                 splits = max(1, min(key_tiles // 2, -(-2 * self.sm_count // blocks), 64))
         floats = self.lib.mb_masked_attention_scratch_floats(tokens, heads, maps, vdim, splits)
         scratch = self._scratch_for(floats) if floats else None
-        check(self.lib.mb_masked_attention(
-            _ptr(q), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), cache.table.shape[1],
-            _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token), _ptr(sinks), _ptr(out),
-            _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens, batch.num_seqs,
-            batch.max_q_len, heads, kv_heads, maps, dim, vdim, cache.page_size, float(scale),
-            float(softcap), self.MASK_KINDS[kind], int(size), int(keep_first), float(lam),
-            float(sub_eps), float(out_scale), splits, _flag(q.dtype), self._stream()),
-            "masked_attention")
+        common = (_ptr(q), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), cache.table.shape[1],
+                  _ptr(batch.q_start), _ptr(batch.kv_len), _ptr(batch.seq_of_token), _ptr(sinks),
+                  _ptr(out), _ptr(scratch), scratch.numel() if scratch is not None else 0, tokens,
+                  batch.num_seqs, batch.max_q_len, heads, kv_heads, maps, dim, vdim, cache.page_size,
+                  float(scale), float(softcap), self.MASK_KINDS[kind], int(size), int(keep_first),
+                  float(lam), float(sub_eps), float(out_scale), splits)
+        if use_mma:
+            check(self.lib.mb_masked_attention_mma(*common, self._stream()), "masked_attention (mma)")
+        else:
+            check(self.lib.mb_masked_attention(*common, _flag(q.dtype), self._stream()),
+                  "masked_attention")
         self.launches += 1 if splits == 1 else 2
 
     # ------------------------------------------------------------------ retention
