@@ -902,8 +902,8 @@ def lizazen_config(size: str) -> dict:
     attention with a dense feed-forward, and chunked attention beside retention with routed
     experts, twice over."""
     width, heads, kv_heads, dim, ff, experts, top, window, keep = LIZAZEN_SIZES[size]
-    moe = {"kind": "moe", "expert": {"ff": ff // (top + 1)}, "router": {"experts": experts, "top": top},
-           "shared": {"ff": ff // (top + 1)}}
+    moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top - 1},
+           "shared": {"ff": ff // top}}
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
     capped = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
               "softcap": 50.0, "mask": {"size": window},

@@ -212,25 +212,16 @@ masked_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
             page_s[tid] = page;
         }
         __syncthreads();
-        for (int idx = tid; idx < MK_KEYS * dk; idx += blockDim.x) {
-            const int j = idx / dk, c = idx - j * dk;
+        {
+            // eight threads a key: the page and the slot are looked up once, no division a number
+            const int j = tid >> 3, sub = tid & 7;
             const int page = page_s[j];
-            float kv = 0.f;
-            if (page >= 0) {
-                const int key = kt * MK_KEYS + j;
-                kv = to_float(k_pages[(((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * dk + c]);
-            }
-            k_s[j * (dk + 1) + c] = kv;
-        }
-        for (int idx = tid; idx < MK_KEYS * dv; idx += blockDim.x) {
-            const int j = idx / dv, c = idx - j * dv;
-            const int page = page_s[j];
-            float vv = 0.f;
-            if (page >= 0) {
-                const int key = kt * MK_KEYS + j;
-                vv = to_float(v_pages[(((int64_t)page * n_kv + kvh) * page_size + (key % page_size)) * dv + c]);
-            }
-            v_s[idx] = vv;
+            const int key = kt * MK_KEYS + j;
+            const int64_t at = page >= 0 ? ((int64_t)page * n_kv + kvh) * page_size + (key % page_size) : 0;
+            const T* kp = k_pages + at * dk;
+            const T* vp = v_pages + at * dv;
+            for (int c = sub; c < dk; c += 8) k_s[j * (dk + 1) + c] = page >= 0 ? to_float(kp[c]) : 0.f;
+            for (int c = sub; c < dv; c += 8) v_s[j * dv + c] = page >= 0 ? to_float(vp[c]) : 0.f;
         }
         __syncthreads();
         const int key = kt * MK_KEYS + lane;

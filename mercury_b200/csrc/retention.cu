@@ -8,17 +8,24 @@
 // A block takes one head of one sequence and 32 of its dv columns; a column is held by 8
 // lanes, each with a run of ceil(d / 8) rows in registers (the state lies column by column,
 // [head][column][row], so a lane's run is contiguous in memory). The step's tokens of the
-// sequence are staged 16 at a time in shared memory, rotated and scaled on the way; per
-// token a lane updates its rows and adds up its share of the read-out, and three shuffles
-// finish the column's sum. The walk of a column is the same whatever else is in the batch
+// sequence are staged 32 at a time (16 for key sizes above 128) by asynchronous copies a tile
+// ahead of the walk, with the rows of the rotation tables they need, and rotated and scaled
+// in shared memory; per token a lane updates its rows and adds up its share of the read-out,
+// and three shuffles finish the column's sum. The walk of a column is the same whatever else is in the batch
 // and however the prompt was cut.
 #include "common.cuh"
 
 namespace mb {
 
-constexpr int RT_TOKENS = 16;
 constexpr int RT_COLS = 32;
 
+__device__ __forceinline__ void rt_copy4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+
+// One staged tile of `tt_max` tokens: q and k as projected [tt][d] each, v [tt][RT_COLS], and the
+// tokens' cosines and sines [tt][pairs] each.
 template <int RMAX>
 __global__ void __launch_bounds__(256)
 retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k, int at_v,
@@ -26,12 +33,12 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dim,
                       int interleaved, const int* __restrict__ positions, float* __restrict__ cells,
                       int64_t cell_stride, const int* __restrict__ q_start,
-                      const int* __restrict__ slots, float* __restrict__ out, int heads, int d, int dv) {
+                      const int* __restrict__ slots, float* __restrict__ out, int heads, int d, int dv,
+                      int tt_max) {
     grid_dependency_sync();
     extern __shared__ float rt_smem[];
-    float* q_s = rt_smem;                       // [RT_TOKENS][d]
-    float* k_s = q_s + RT_TOKENS * d;           // [RT_TOKENS][d]
-    float* v_s = k_s + RT_TOKENS * d;           // [RT_TOKENS][RT_COLS]
+    const int pairs = rot_dim / 2;
+    const int tile_floats = tt_max * (2 * d + RT_COLS + 2 * pairs);
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * RT_COLS;
     const int begin = q_start[seq], end = q_start[seq + 1];
     if (end <= begin) return;
@@ -44,40 +51,73 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
     float S[RMAX];
 #pragma unroll
     for (int i = 0; i < RMAX; ++i) S[i] = (i < per && r0 + i < d && p < dv) ? cell[r0 + i] : 0.f;
-    const int pairs = rot_dim / 2;
 
-    for (int t0 = begin; t0 < end; t0 += RT_TOKENS) {
-        const int count = end - t0 < RT_TOKENS ? end - t0 : RT_TOKENS;
-        __syncthreads();
-        // q and k of the tile's tokens, rotated; k also scaled
-        for (int idx = tid; idx < count * 2 * d; idx += blockDim.x) {
-            const int tt = idx / (2 * d), rest = idx - tt * 2 * d;
-            const int which = rest / d, c = rest - which * d;
-            const float* x = pre + (int64_t)(t0 + tt) * ld + (which ? at_k : at_q) + head * d;
-            float val;
-            if (c < rot_dim) {
-                int i, other;
-                bool first;
-                if (interleaved) {
-                    i = c >> 1, first = !(c & 1), other = first ? c + 1 : c - 1;
-                } else {
-                    first = c < pairs, i = first ? c : c - pairs, other = first ? c + pairs : c - pairs;
-                }
-                const int pos = checked_position(positions[t0 + tt]);
-                const float cs = cos_t[(int64_t)pos * pairs + i], sn = sin_t[(int64_t)pos * pairs + i];
-                val = first ? x[c] * cs - x[other] * sn : x[c] * cs + x[other] * sn;
-            } else {
-                val = x[c];
+    // a tile's rows are brought by 4-byte asynchronous copies a tile ahead of the walk: a thread
+    // owns a token of the tile (16 threads a token) and strides over its numbers
+    const int lanes_per_token = 256 / tt_max;           // 8 (32 tokens a tile) or 16
+    const int my_tt = tid / lanes_per_token, my_l = tid - my_tt * lanes_per_token;
+    auto issue = [&](int t0, float* buf) {
+        const int count = end - t0 < tt_max ? end - t0 : tt_max;
+        if (my_tt < count) {
+            const int t = t0 + my_tt;
+            const float* row = pre + (int64_t)t * ld;
+            float* q_b = buf + my_tt * d;
+            float* k_b = buf + tt_max * d + my_tt * d;
+            for (int c = my_l; c < d; c += lanes_per_token) {
+                rt_copy4(q_b + c, row + at_q + head * d + c);
+                rt_copy4(k_b + c, row + at_k + head * d + c);
             }
-            (which ? k_s : q_s)[tt * d + c] = which ? val * key_scale : val;
+            float* v_b = buf + 2 * tt_max * d + my_tt * RT_COLS;
+            for (int c = my_l; c < RT_COLS; c += lanes_per_token)
+                if (col0 + c < dv) rt_copy4(v_b + c, row + at_v + head * dv + col0 + c);
+            if (pairs > 0) {
+                const int64_t pos = checked_position(positions[t]);
+                float* c_b = buf + tt_max * (2 * d + RT_COLS) + my_tt * pairs;
+                float* s_b = c_b + tt_max * pairs;
+                for (int i = my_l; i < pairs; i += lanes_per_token) {
+                    rt_copy4(c_b + i, cos_t + pos * pairs + i);
+                    rt_copy4(s_b + i, sin_t + pos * pairs + i);
+                }
+            }
         }
-        for (int idx = tid; idx < count * RT_COLS; idx += blockDim.x) {
-            const int tt = idx / RT_COLS, c = idx - tt * RT_COLS;
-            v_s[idx] = col0 + c < dv ? pre[(int64_t)(t0 + tt) * ld + at_v + head * dv + col0 + c] : 0.f;
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    issue(begin, rt_smem);
+    int turn = 0;
+    for (int t0 = begin; t0 < end; t0 += tt_max, turn ^= 1) {
+        const int count = end - t0 < tt_max ? end - t0 : tt_max;
+        float* buf = rt_smem + turn * tile_floats;
+        if (t0 + tt_max < end) {
+            issue(t0 + tt_max, rt_smem + (turn ^ 1) * tile_floats);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();
+        float* q_s = buf;
+        float* k_s = buf + tt_max * d;
+        const float* v_s = buf + 2 * tt_max * d;
+        // in place: the rotation of q and k (a thread takes whole pairs), then the keys' scale
+        if (my_tt < count) {
+            const float* c_b = buf + tt_max * (2 * d + RT_COLS) + my_tt * pairs;
+            const float* s_b = c_b + tt_max * pairs;
+            for (int i = my_l; i < pairs; i += lanes_per_token) {
+                const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + pairs;
+                const float cs = c_b[i], sn = s_b[i];
+                float* qr = q_s + my_tt * d;
+                float* kr = k_s + my_tt * d;
+                const float qa = qr[a], qb = qr[b], ka = kr[a], kb = kr[b];
+                qr[a] = qa * cs - qb * sn;
+                qr[b] = qb * cs + qa * sn;
+                kr[a] = (ka * cs - kb * sn) * key_scale;
+                kr[b] = (kb * cs + ka * sn) * key_scale;
+            }
+            for (int c = rot_dim + my_l; c < d; c += lanes_per_token) k_s[my_tt * d + c] *= key_scale;
         }
         __syncthreads();
         for (int tt = 0; tt < count; ++tt) {
-            const float v = v_s[tt * RT_COLS + col];
+            const float v = p < dv ? v_s[tt * RT_COLS + col] : 0.f;
             const float* kr = k_s + tt * d + r0;
             const float* qr = q_s + tt * d + r0;
             float o = 0.f;
@@ -93,6 +133,7 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
             o += __shfl_xor_sync(0xffffffffu, o, 4);
             if (sub == 0 && p < dv) out[(int64_t)(t0 + tt) * heads * dv + head * dv + p] = o;
         }
+        __syncthreads();      // the tile is free for the copies of the tile after next
     }
     if (p < dv) {
 #pragma unroll
@@ -121,12 +162,24 @@ MB_EXPORT int mb_retention_scan(const float* pre, int ld, int at_q, int at_k, in
     const int col_blocks = (dv + RT_COLS - 1) / RT_COLS;
     if (col_blocks > 65535) return MB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(num_seqs, heads, col_blocks);
-    const size_t smem = (size_t)(2 * RT_TOKENS * d + RT_TOKENS * RT_COLS) * sizeof(float);
+    // two tiles of 32 tokens (16 for key sizes above 128) in shared memory
+    const int tt_max = d <= 128 ? 32 : 16;
+    const size_t smem = (size_t)2 * tt_max * (2 * d + RT_COLS + rot_dim) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
 #define MB_RT_CASE(R)                                                                              \
-    MB_LAUNCH((retention_scan_kernel<R>), grid, 256, smem, s, pre, ld, at_q, at_k, at_v, decay,     \
-              key_scale, cos_t, sin_t, rot_dim, interleaved, positions, cells, (int64_t)cell_stride, \
-              q_start, slots, out, heads, d, dv)
+    do {                                                                                           \
+        static size_t raised = 0;                                                                  \
+        if (smem > 40 * 1024 && smem > raised) {                                                   \
+            if (cudaFuncSetAttribute(retention_scan_kernel<R>,                                     \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=    \
+                cudaSuccess)                                                                       \
+                return MB_ERR_UNSUPPORTED_SIZE;                                                    \
+            raised = smem;                                                                         \
+        }                                                                                          \
+        MB_LAUNCH((retention_scan_kernel<R>), grid, 256, smem, s, pre, ld, at_q, at_k, at_v, decay, \
+                  key_scale, cos_t, sin_t, rot_dim, interleaved, positions, cells,                 \
+                  (int64_t)cell_stride, q_start, slots, out, heads, d, dv, tt_max);                \
+    } while (0)
     if (d <= 32) MB_RT_CASE(4);
     else if (d <= 64) MB_RT_CASE(8);
     else if (d <= 128) MB_RT_CASE(16);

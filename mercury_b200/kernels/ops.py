@@ -901,7 +901,9 @@ class CudaOps:
         if kernel == "mma" and not mma_ok:
             raise KernelError(f"the tensor-core sigmoid attention takes bfloat16 with head size 64 or "
                               f"128, not {q.dtype} with {dim}")
-        use_mma = mma_ok and (kernel == "mma" or (kernel is None and batch.max_q_len * group >= 64))
+        # (decode steps too: few of a tile's 64 rows are live there, but its keys and values come
+        # by 16-byte asynchronous copies two tiles deep, which is what a decode step waits for)
+        use_mma = mma_ok and kernel in (None, "mma")
         rows, keys = (64, 64) if use_mma else (16, 32)
         # the keys a row looks at are bounded by the window; divide them when the batch alone
         # cannot fill the device
