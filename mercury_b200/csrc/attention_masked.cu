@@ -320,7 +320,10 @@ masked_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 
 // The parts of a (token, head) merged, split 0 first: per map the largest maximum (the sink's
 // number included), the sums and the weighted values brought to it; then, with two maps,
-// their difference and its norm. One warp per (token, head).
+// their difference and its norm. A block per (token, head), a thread per value column: the
+// first warp reads the parts' maxima and sums side by side (a lane a part) and leaves a
+// weight per part, then every thread adds up its column over the parts, whose reads do not
+// wait for one another.
 template <typename T, int MAPS>
 __global__ void masked_attention_merge_kernel(const float* __restrict__ part_acc,
                                               const float* __restrict__ part_ml,
@@ -329,43 +332,55 @@ __global__ void masked_attention_merge_kernel(const float* __restrict__ part_acc
                                               int n_q, int dv, int num_splits, float lambda,
                                               float sub_eps, float out_scale) {
     grid_dependency_sync();
-    extern __shared__ float o_s[];          // [dv]
+    extern __shared__ float w_s[];          // [MAPS][num_splits] weights, then [MAPS] 1 / sum
+    __shared__ float scratch[33];
+    float* inv_s = w_s + MAPS * num_splits;
     const int tok = blockIdx.x, head = blockIdx.y;
-    const int lane = threadIdx.x;
+    const int c = threadIdx.x, lane = c & 31;
     const int64_t flat = (int64_t)tok * n_q + head;
     if (seq_of_token[tok] < 0) {
-        for (int c = lane; c < dv; c += 32) out[flat * dv + c] = from_float<T>(0.f);
+        if (c < dv) out[flat * dv + c] = from_float<T>(0.f);
         return;
     }
-    for (int mp = 0; mp < MAPS; ++mp) {
-        float m = sinks != nullptr ? sinks[head] : -INFINITY;
-        for (int z = 0; z < num_splits; ++z)
-            m = fmaxf(m, part_ml[((flat * num_splits + z) * MAPS + mp) * 2]);
-        float l = sinks != nullptr ? expf(sinks[head] - m) : 0.f;
-        for (int z = 0; z < num_splits; ++z) {
-            const int64_t at = (flat * num_splits + z) * MAPS + mp;
-            l += part_ml[at * 2 + 1] * expf(part_ml[at * 2] - m);
-        }
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        for (int c = lane; c < dv; c += 32) {
-            float a = 0.f;
-            for (int z = 0; z < num_splits; ++z) {
+    if (c < 32) {
+#pragma unroll
+        for (int mp = 0; mp < MAPS; ++mp) {
+            const float sink = sinks != nullptr ? sinks[head] : -INFINITY;
+            float m = sink;
+            for (int z = lane; z < num_splits; z += 32)
+                m = fmaxf(m, part_ml[((flat * num_splits + z) * MAPS + mp) * 2]);
+            m = warp_max(m);
+            float l = 0.f;
+            for (int z = lane; z < num_splits; z += 32) {
                 const int64_t at = (flat * num_splits + z) * MAPS + mp;
-                const float w = expf(part_ml[at * 2] - m);
-                if (w != 0.f) a = fmaf(part_acc[at * dv + c], w, a);
+                const float mz = part_ml[at * 2];
+                const float w = mz == -INFINITY ? 0.f : expf(mz - m);
+                w_s[mp * num_splits + z] = w;
+                l = fmaf(part_ml[at * 2 + 1], w, l);
             }
-            a *= inv;
-            o_s[c] = mp == 0 ? a : o_s[c] - lambda * a;
+            l = warp_sum(l);
+            if (sinks != nullptr) l += expf(sink - m);
+            if (lane == 0) inv_s[mp] = l > 0.f ? 1.f / l : 0.f;
         }
     }
-    float r = 1.f;
-    if (MAPS == 2) {
-        float ss = 0.f;
-        for (int c = lane; c < dv; c += 32) ss = fmaf(o_s[c], o_s[c], ss);
-        ss = warp_sum(ss);
-        r = out_scale / sqrtf(ss / (float)dv + sub_eps);
+    __syncthreads();
+    float o = 0.f;
+    if (c < dv) {
+#pragma unroll
+        for (int mp = 0; mp < MAPS; ++mp) {
+            float a = 0.f;
+#pragma unroll 8
+            for (int z = 0; z < num_splits; ++z)
+                a = fmaf(part_acc[((flat * num_splits + z) * MAPS + mp) * dv + c], w_s[mp * num_splits + z], a);
+            a *= inv_s[mp];
+            o = mp == 0 ? a : o - lambda * a;
+        }
     }
-    for (int c = lane; c < dv; c += 32) out[flat * dv + c] = from_float<T>(o_s[c] * r);
+    if (MAPS == 2) {
+        const float ss = block_sum(c < dv ? o * o : 0.f, scratch);
+        o *= out_scale / sqrtf(ss / (float)dv + sub_eps);
+    }
+    if (c < dv) out[flat * dv + c] = from_float<T>(o);
 }
 
 struct MaskedArgs {
@@ -405,7 +420,8 @@ int launch_masked(const MaskedArgs& a, cudaStream_t s) {
     if (launch_status() != MB_OK) return MB_ERR_LAUNCH;
     if (a.num_splits == 1) return MB_OK;
     dim3 mgrid(a.tokens, a.n_q);
-    MB_LAUNCH((masked_attention_merge_kernel<T, MAPS>), mgrid, 32, (size_t)a.dv * sizeof(float), s,
+    MB_LAUNCH((masked_attention_merge_kernel<T, MAPS>), mgrid, (a.dv + 31) / 32 * 32,
+              (size_t)(MAPS * a.num_splits + MAPS) * sizeof(float), s,
               a.part_acc, a.part_ml, a.seq_of_token, a.sinks, (T*)a.out, a.n_q, a.dv, a.num_splits,
               a.lambda, a.sub_eps, a.out_scale);
     return launch_status();
@@ -756,7 +772,8 @@ int launch_masked_mma(const MaskedArgs& a, cudaStream_t s) {
     if (launch_status() != MB_OK) return MB_ERR_LAUNCH;
     if (a.num_splits == 1) return MB_OK;
     dim3 mgrid(a.tokens, a.n_q);
-    MB_LAUNCH((masked_attention_merge_kernel<bf, MAPS>), mgrid, 32, (size_t)DV * sizeof(float), s, a.part_acc,
+    MB_LAUNCH((masked_attention_merge_kernel<bf, MAPS>), mgrid, DV, (size_t)(MAPS * a.num_splits + MAPS) * sizeof(float), s,
+              a.part_acc,
               a.part_ml, a.seq_of_token, a.sinks, (bf*)a.out, a.n_q, DV, a.num_splits, a.lambda, a.sub_eps,
               a.out_scale);
     return launch_status();

@@ -51,7 +51,20 @@ struct SkinnyInput {
     int ss_tiles;
     float ss_eps;
     int ss_k;
+    // the gate of the gated form: 0 = silu(gate) * up; 2 = the clamped sigmoid gate, g sigmoid(
+    // gate_slope g) (u + 1) of g = min(gate, gate_limit) and u = clamp(up, -gate_limit, gate_limit)
+    int gate_act;
+    float gate_limit, gate_slope;
 };
+
+__device__ __forceinline__ float skinny_gated(const SkinnyInput& in, float gate, float up) {
+    if (in.gate_act == 2) {
+        const float g = fminf(gate, in.gate_limit);
+        const float u = fminf(fmaxf(up, -in.gate_limit), in.gate_limit);
+        return g / (1.f + expf(-in.gate_slope * g)) * (u + 1.f);
+    }
+    return gate / (1.f + expf(-gate)) * up;
+}
 
 // 1/rms of each row from the partial sums of squares, into scale_s[T] (ones without them).
 __device__ __forceinline__ void skinny_row_scale(const SkinnyInput& in, int T, float* scale_s) {
@@ -351,7 +364,7 @@ skinny_gemm_kernel(SkinnyInput in_all,
             gate = __bfloat162float(__float2bfloat16_rn(gate * scale_s[tok]));
             up = __bfloat162float(__float2bfloat16_rn(up * scale_s[tok]));
             reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * half_n + n] =
-                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                __float2bfloat16_rn(skinny_gated(in, gate, up));
         }
     } else {
         // (the loop bound and the block size are multiples of 32: whole warps run it, and
@@ -534,7 +547,7 @@ skinny_fed_kernel(const __grid_constant__ CUtensorMap wmap, SkinnyInput in_all,
             gate = __bfloat162float(__float2bfloat16_rn(gate * scale_s[tok]));
             up = __bfloat162float(__float2bfloat16_rn(up * scale_s[tok]));
             reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * half_n + n] =
-                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                __float2bfloat16_rn(skinny_gated(in, gate, up));
         }
     } else {
         for (int idx = threadIdx.x; idx < rowt * 16 * TOK; idx += blockDim.x) {
@@ -805,6 +818,9 @@ static SkinnyInput skinny_input(const void* x, const float* h, const void* norm_
     in.ss_tiles = ss_tiles;
     in.ss_eps = ss_eps;
     in.ss_k = ss_k;
+    in.gate_act = 0;
+    in.gate_limit = 0.f;
+    in.gate_slope = 1.f;
     return in;
 }
 
@@ -942,13 +958,18 @@ MB_EXPORT int mb_gemm_skinny_swiglu(const void* x, const float* h, const void* n
                                     const int* rows, float eps, const float* ss_part, int ss_tiles,
                                     float ss_eps, int ss_k, const void* w, void* out, int T,
                                     int width, int K, const void* ahead, long long ahead_bytes,
-                                    int* error, void* stream) {
+                                    int gate_act, float gate_limit, float gate_slope, int* error,
+                                    void* stream) {
     // ahead, ahead_bytes: the matrix that the product behind this one will stream (or null):
     // L2 is asked for it once this product's own weights are in
     if (!mb_gemm_skinny_supports(T, width, K)) return MB_ERR_UNSUPPORTED_SIZE;
     typedef __nv_bfloat16 bf;
     cudaStream_t s = (cudaStream_t)stream;
-    const SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
+    if (gate_act != 0 && gate_act != 2) return MB_ERR_UNSUPPORTED_SIZE;
+    SkinnyInput in = skinny_input(x, h, norm_w, rows, eps, ss_part, ss_tiles, ss_eps, ss_k);
+    in.gate_act = gate_act;
+    in.gate_limit = gate_limit;
+    in.gate_slope = gate_slope;
     if (T <= 16 && g_fed_min_elements > 0 && 2ll * width * K >= (g_fed_min_elements > g_fed_min_gated || g_fed_min_elements < 1024 ? g_fed_min_elements : g_fed_min_gated)) {
         const int rc_fed = launch_fed(in, w, nullptr, out, 0, T, 2 * width, K, width / 16, nullptr, nullptr,
                                       nullptr, error, s);

@@ -24,9 +24,16 @@ __device__ __forceinline__ void rt_copy4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
 }
 
+__device__ __forceinline__ void rt_copy16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
+}
+
 // One staged tile of `tt_max` tokens: q and k as projected [tt][d] each, v [tt][RT_COLS], and the
 // tokens' cosines and sines [tt][pairs] each.
-template <int RMAX>
+// RMAX: the rows a lane can hold; EXACT: d is 8 * RMAX (a lane's run is full and starts on a
+// 16-byte boundary), so the walk needs no bounds and reads q and k four numbers at a time.
+template <int RMAX, bool EXACT>
 __global__ void __launch_bounds__(256)
 retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k, int at_v,
                       const float* __restrict__ decay, float key_scale,
@@ -34,9 +41,9 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
                       int interleaved, const int* __restrict__ positions, float* __restrict__ cells,
                       int64_t cell_stride, const int* __restrict__ q_start,
                       const int* __restrict__ slots, float* __restrict__ out, int heads, int d, int dv,
-                      int tt_max) {
+                      int tt_max, int wide) {
     grid_dependency_sync();
-    extern __shared__ float rt_smem[];
+    extern __shared__ __align__(16) float rt_smem[];
     const int pairs = rot_dim / 2;
     const int tile_floats = tt_max * (2 * d + RT_COLS + 2 * pairs);
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * RT_COLS;
@@ -52,8 +59,9 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
 #pragma unroll
     for (int i = 0; i < RMAX; ++i) S[i] = (i < per && r0 + i < d && p < dv) ? cell[r0 + i] : 0.f;
 
-    // a tile's rows are brought by 4-byte asynchronous copies a tile ahead of the walk: a thread
-    // owns a token of the tile (16 threads a token) and strides over its numbers
+    // a tile's rows are brought by asynchronous copies a tile ahead of the walk, 16 bytes a copy
+    // where every offset allows (`wide`), else 4: a thread owns a token of the tile (8 or 16
+    // threads a token) and strides over its numbers
     const int lanes_per_token = 256 / tt_max;           // 8 (32 tokens a tile) or 16
     const int my_tt = tid / lanes_per_token, my_l = tid - my_tt * lanes_per_token;
     auto issue = [&](int t0, float* buf) {
@@ -63,17 +71,28 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
             const float* row = pre + (int64_t)t * ld;
             float* q_b = buf + my_tt * d;
             float* k_b = buf + tt_max * d + my_tt * d;
-            for (int c = my_l; c < d; c += lanes_per_token) {
-                rt_copy4(q_b + c, row + at_q + head * d + c);
-                rt_copy4(k_b + c, row + at_k + head * d + c);
-            }
             float* v_b = buf + 2 * tt_max * d + my_tt * RT_COLS;
-            for (int c = my_l; c < RT_COLS; c += lanes_per_token)
-                if (col0 + c < dv) rt_copy4(v_b + c, row + at_v + head * dv + col0 + c);
-            if (pairs > 0) {
-                const int64_t pos = checked_position(positions[t]);
-                float* c_b = buf + tt_max * (2 * d + RT_COLS) + my_tt * pairs;
-                float* s_b = c_b + tt_max * pairs;
+            float* c_b = buf + tt_max * (2 * d + RT_COLS) + my_tt * pairs;
+            float* s_b = c_b + tt_max * pairs;
+            const int64_t pos = pairs > 0 ? checked_position(positions[t]) : 0;
+            if (wide) {
+                for (int c = my_l * 4; c < d; c += lanes_per_token * 4) {
+                    rt_copy16(q_b + c, row + at_q + head * d + c);
+                    rt_copy16(k_b + c, row + at_k + head * d + c);
+                }
+                for (int c = my_l * 4; c < RT_COLS; c += lanes_per_token * 4)
+                    if (col0 + c < dv) rt_copy16(v_b + c, row + at_v + head * dv + col0 + c);
+                for (int i = my_l * 4; i < pairs; i += lanes_per_token * 4) {
+                    rt_copy16(c_b + i, cos_t + pos * pairs + i);
+                    rt_copy16(s_b + i, sin_t + pos * pairs + i);
+                }
+            } else {
+                for (int c = my_l; c < d; c += lanes_per_token) {
+                    rt_copy4(q_b + c, row + at_q + head * d + c);
+                    rt_copy4(k_b + c, row + at_k + head * d + c);
+                }
+                for (int c = my_l; c < RT_COLS; c += lanes_per_token)
+                    if (col0 + c < dv) rt_copy4(v_b + c, row + at_v + head * dv + col0 + c);
                 for (int i = my_l; i < pairs; i += lanes_per_token) {
                     rt_copy4(c_b + i, cos_t + pos * pairs + i);
                     rt_copy4(s_b + i, sin_t + pos * pairs + i);
@@ -116,16 +135,35 @@ retention_scan_kernel(const float* __restrict__ pre, int ld, int at_q, int at_k,
             for (int c = rot_dim + my_l; c < d; c += lanes_per_token) k_s[my_tt * d + c] *= key_scale;
         }
         __syncthreads();
+#pragma unroll 4
         for (int tt = 0; tt < count; ++tt) {
             const float v = p < dv ? v_s[tt * RT_COLS + col] : 0.f;
             const float* kr = k_s + tt * d + r0;
             const float* qr = q_s + tt * d + r0;
             float o = 0.f;
+            if (EXACT) {
+                float o2 = 0.f;          // two partial sums: half as long a chain of additions
 #pragma unroll
-            for (int i = 0; i < RMAX; ++i) {
-                if (i < per && r0 + i < d) {
-                    S[i] = fmaf(g, S[i], kr[i] * v);
-                    o = fmaf(S[i], qr[i], o);
+                for (int i = 0; i < RMAX; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+                    S[i] = fmaf(g, S[i], k4.x * v);
+                    S[i + 1] = fmaf(g, S[i + 1], k4.y * v);
+                    S[i + 2] = fmaf(g, S[i + 2], k4.z * v);
+                    S[i + 3] = fmaf(g, S[i + 3], k4.w * v);
+                    o = fmaf(S[i], q4.x, o);
+                    o2 = fmaf(S[i + 1], q4.y, o2);
+                    o = fmaf(S[i + 2], q4.z, o);
+                    o2 = fmaf(S[i + 3], q4.w, o2);
+                }
+                o += o2;
+            } else {
+#pragma unroll
+                for (int i = 0; i < RMAX; ++i) {
+                    if (i < per && r0 + i < d) {
+                        S[i] = fmaf(g, S[i], kr[i] * v);
+                        o = fmaf(S[i], qr[i], o);
+                    }
                 }
             }
             o += __shfl_xor_sync(0xffffffffu, o, 1);
@@ -165,20 +203,34 @@ MB_EXPORT int mb_retention_scan(const float* pre, int ld, int at_q, int at_k, in
     // two tiles of 32 tokens (16 for key sizes above 128) in shared memory
     const int tt_max = d <= 128 ? 32 : 16;
     const size_t smem = (size_t)2 * tt_max * (2 * d + RT_COLS + rot_dim) * sizeof(float);
+    // 16-byte copies need every row piece to start on a 16-byte boundary
+    const int pairs = rot_dim / 2;
+    const int wide = (d % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && at_q % 4 == 0 && at_k % 4 == 0 &&
+                      at_v % 4 == 0 && pairs % 4 == 0 && ((uintptr_t)pre & 15) == 0 &&
+                      (pairs == 0 || ((((uintptr_t)cos_t) | ((uintptr_t)sin_t)) & 15) == 0))
+                         ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
 #define MB_RT_CASE(R)                                                                              \
     do {                                                                                           \
         static size_t raised = 0;                                                                  \
         if (smem > 40 * 1024 && smem > raised) {                                                   \
-            if (cudaFuncSetAttribute(retention_scan_kernel<R>,                                     \
+            if (cudaFuncSetAttribute(retention_scan_kernel<R, true>,                               \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=    \
-                cudaSuccess)                                                                       \
+                    cudaSuccess ||                                                                 \
+                cudaFuncSetAttribute(retention_scan_kernel<R, false>,                              \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=    \
+                    cudaSuccess)                                                                   \
                 return MB_ERR_UNSUPPORTED_SIZE;                                                    \
             raised = smem;                                                                         \
         }                                                                                          \
-        MB_LAUNCH((retention_scan_kernel<R>), grid, 256, smem, s, pre, ld, at_q, at_k, at_v, decay, \
-                  key_scale, cos_t, sin_t, rot_dim, interleaved, positions, cells,                 \
-                  (int64_t)cell_stride, q_start, slots, out, heads, d, dv, tt_max);                \
+        if (d == 8 * R)                                                                            \
+            MB_LAUNCH((retention_scan_kernel<R, true>), grid, 256, smem, s, pre, ld, at_q, at_k, at_v, \
+                      decay, key_scale, cos_t, sin_t, rot_dim, interleaved, positions, cells,      \
+                      (int64_t)cell_stride, q_start, slots, out, heads, d, dv, tt_max, wide);            \
+        else                                                                                       \
+            MB_LAUNCH((retention_scan_kernel<R, false>), grid, 256, smem, s, pre, ld, at_q, at_k, at_v, \
+                      decay, key_scale, cos_t, sin_t, rot_dim, interleaved, positions, cells,      \
+                      (int64_t)cell_stride, q_start, slots, out, heads, d, dv, tt_max, wide);            \
     } while (0)
     if (d <= 32) MB_RT_CASE(4);
     else if (d <= 64) MB_RT_CASE(8);

@@ -570,13 +570,16 @@ class CudaOps:
         return held[1]
 
     @_timed("gated product")
-    def linear_swiglu(self, x, weight, out, ctx, ahead=None):
+    def linear_swiglu(self, x, weight, out, ctx, ahead=None, gate=None):
         """out = silu(x . gate^T) * (x . up^T) for `weight` = [gate rows; up rows]: one kernel
         for few tokens, product then gate otherwise. `ahead`: the matrix that the product
         behind this one will stream; the few-token kernel asks L2 for it once its own weights
         are in (`look_ahead_max_bytes` bounds what is asked for)."""
         m, k = x.shape
         width = out.shape[1]
+        # `gate` = (limit, slope): the clamped sigmoid gate in place of SiLU, which only the
+        # few-token kernel has fused (None is returned when this call is not for it)
+        form = (0, 0.0, 1.0) if gate is None else (2, float(gate[0]), float(gate[1]))
         if (self.skinny and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                 and self.lib.mb_gemm_skinny_supports(m, width, k)
                 and 2 * width * k <= self.skinny_max_elements):
@@ -587,12 +590,14 @@ class CudaOps:
                 bytes_ahead = ahead.numel() * ahead.element_size()
             check(self.lib.mb_gemm_skinny_swiglu(*self._skinny_input(x), _ptr(weight), _ptr(out),
                                                  m, width, k, _ptr(ahead) if bytes_ahead else None,
-                                                 bytes_ahead, _ptr(self._error_word()),
+                                                 bytes_ahead, *form, _ptr(self._error_word()),
                                                  self._stream()),
                   "linear_swiglu (skinny)")
             self.launches += 1
             self._tc_pending = self._tc_pending or 2 * width * k >= self.fed_min_elements
-            return
+            return True
+        if gate is not None:
+            return None
         if self._pending(x) is not None:
             x = x.materialize()
         if (self.gemm in ("tcgen05", "auto") and x.dtype == torch.bfloat16
@@ -626,6 +631,9 @@ class CudaOps:
             return self.linear_swiglu(x, weight, out, ctx)
         if activation not in ("gelu_tanh", "clamped_sigmoid"):
             raise KernelError(f"no gate kernel for the activation {activation!r}")
+        if activation == "clamped_sigmoid" and self.linear_swiglu(x, weight, out, ctx,
+                                                                  gate=(limit, slope)):
+            return           # few tokens: product and gate in one kernel
         if self._pending(x) is not None:
             x = x.materialize()
         m, width = x.shape[0], out.shape[1]
@@ -901,9 +909,7 @@ class CudaOps:
         if kernel == "mma" and not mma_ok:
             raise KernelError(f"the tensor-core sigmoid attention takes bfloat16 with head size 64 or "
                               f"128, not {q.dtype} with {dim}")
-        # (decode steps too: few of a tile's 64 rows are live there, but its keys and values come
-        # by 16-byte asynchronous copies two tiles deep, which is what a decode step waits for)
-        use_mma = mma_ok and kernel in (None, "mma")
+        use_mma = mma_ok and (kernel == "mma" or (kernel is None and batch.max_q_len * group >= 64))
         rows, keys = (64, 64) if use_mma else (16, 32)
         # the keys a row looks at are bounded by the window; divide them when the batch alone
         # cannot fill the device
@@ -978,7 +984,9 @@ class CudaOps:
         if kernel == "mma" and not mma_ok:
             raise KernelError(f"the tensor-core masked attention takes bfloat16 with key and value "
                               f"sizes of 64 or 128, not {q.dtype} with {maps} x {dim} and {vdim}")
-        use_mma = mma_ok and (kernel == "mma" or (kernel is None and batch.max_q_len * group >= 64))
+        # (decode steps too: few of a tile's 64 rows are live there, but its keys and values come
+        # by 16-byte asynchronous copies two tiles deep, which is what a decode step waits for)
+        use_mma = mma_ok and kernel in (None, "mma")
         rows, keys = (64, 64) if use_mma else (16, 32)
         if getattr(batch, "attention_splits", None):
             splits = batch.attention_splits

@@ -218,6 +218,27 @@ def test_experts_weighted_on_their_input_against_the_twin(ops, twin, dtype, pair
     close(got, want, dtype, "experts", tol32=1e-5, tol16=2e-2)
 
 
+@pytest.mark.parametrize("tokens", [1, 5, 16, 40])
+@pytest.mark.parametrize("hidden,ff", [(256, 96), (896, 4864)])
+def test_clamped_gate_in_the_few_token_product(ops, twin, tokens, hidden, ff):
+    """Up to 16 tokens the product and the clamped gate are one kernel; beyond, two."""
+    from mercury_b200.engine.runner import StepContext, Workspace
+
+    dtype = torch.bfloat16
+    x = rand((tokens, hidden), dtype, 1)
+    weight = rand((2 * ff, hidden), dtype, 2, 0.08)
+    ctx = StepContext(ops, Workspace(torch.device("cuda"), dtype, tokens), 16, dtype)
+    got = torch.zeros((tokens, ff), dtype=dtype, device="cuda")
+    want = torch.zeros_like(got)
+    before = ops.launches + ops.library_calls
+    ops.linear_gated(x, weight, got, ctx, "clamped_sigmoid", limit=0.8, slope=1.702)
+    assert (ops.launches + ops.library_calls - before == 1) == (tokens <= 16)
+    twin.linear_gated(x, weight, want, None, "clamped_sigmoid", limit=0.8, slope=1.702)
+    raw = x.float() @ weight.float().T
+    assert (raw > 0.8).any() and (raw < -0.8).any()
+    close(got, want, dtype, "clamped gate", tol16=1.2e-2)
+
+
 # ------------------------------------------------------------------------------ the model
 
 LENGTHS = {"mix": (37, 70, 129, 45, 3, 66), "ones": (33, 64, 100, 41), "odd": (50, 7, 121, 33),
