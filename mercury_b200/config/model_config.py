@@ -677,8 +677,6 @@ class LizazenConfig(ModelConfig):
             bigram = (positive(bigram, "buckets", "embedding.bigram"),
                       int(need(bigram, "mul_prev", "embedding.bigram")),
                       int(need(bigram, "mul_cur", "embedding.bigram")))
-            if bigram[1] < 0 or bigram[2] < 0:
-                raise ConfigError("embedding.bigram: the multipliers must not be negative")
         return cls(
             architecture=str(raw.get("architecture") or (raw.get("architectures") or ["Lizazen"])[0]),
             width=positive(raw, "width", "the model"),

@@ -56,7 +56,8 @@ __global__ void embed_bigram_kernel(const int* __restrict__ ids, const void* __r
     int row = buckets;
     if (positions[t] > 0) {
         const int prev = t == begin ? state[0] : ids[t - 1];
-        row = (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % buckets);
+        // (multipliers below the bucket count, tokens below 2^31: no 64-bit overflow)
+        row = (int)(((long long)(prev % buckets) * mul_prev + (long long)(id % buckets) * mul_cur) % buckets);
     }
     const int64_t base = (int64_t)id * hidden, pbase = (int64_t)row * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x)

@@ -81,7 +81,12 @@ class BigramEmbedding(TokenEmbedding):
                  buckets: int, mul_prev: int, mul_cur: int):
         super().__init__(vocab_size, hidden_size, weight_name)
         self.pair_name = pair_name
-        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if int(buckets) <= 0 or int(buckets) >= 1 << 31:
+            raise ValueError(f"buckets={buckets} must be positive and below 2^31")
+        # (a x + b y) mod n = ((a mod n) x + (b mod n) y) mod n: the kernel gets multipliers below
+        # the bucket count, so its 64-bit products are exact whatever the configuration names
+        self.buckets = int(buckets)
+        self.mul_prev, self.mul_cur = int(mul_prev) % self.buckets, int(mul_cur) % self.buckets
         self.pair_table = None
 
     def state_need(self):

@@ -630,6 +630,7 @@ class TorchOps:
             for t in range(begin, end):
                 tok = int(ids[t])
                 row = buckets if positions[t] == 0 else (prev * mul_prev + tok * mul_cur) % buckets
+                assert 0 <= mul_prev < buckets and 0 <= mul_cur < buckets
                 pair_rows[t] = pairs[row].to(self.acc)
                 live[t] = True
                 prev = tok

@@ -95,7 +95,13 @@ def weight_on(config, W, prefix, x, query, key, fn):
 def check_bigram_embedding(ops, device, dtype):
     from mercury_b200.parts.embedding import BigramEmbedding
 
-    vocab, width, buckets, mul_prev, mul_cur = 61, 24, 17, 29, 3
+    check_bigram_case(ops, device, dtype, 61, 24, 17, 29, 3)
+    check_bigram_case(ops, device, dtype, 50000, 8, 1000003, 10 ** 15 + 37, -5)     # beyond 64-bit products
+
+
+def check_bigram_case(ops, device, dtype, vocab, width, buckets, mul_prev, mul_cur):
+    from mercury_b200.parts.embedding import BigramEmbedding
+
     part = BigramEmbedding(vocab, width, "embed", "bigram", buckets, mul_prev, mul_cur)
     W = {"embed": rand((vocab, width), 1).bfloat16(), "bigram": rand((buckets + 1, width), 2).bfloat16()}
     stand = Stand(ops, device, dtype)
