@@ -906,12 +906,12 @@ def lizazen_config(size: str) -> dict:
            "shared": {"ff": ff // top}}
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
     capped = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-              "softcap": 50.0, "mask": {"size": window},
-              "rot": {"base": 500000.0, "dims": dim,
-                      "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+              "softcap": 30.0, "mask": {"size": window},
+              "rot": {"base": 100000.0, "dims": dim,
+                      "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 4096}}}
     maps = width // 128
     differential = {"heads": maps, "kv_heads": max(1, maps // 7) if maps % 7 == 0 else 2, "dim": 64,
-                    "vdim": 128, "diff": 0.6, "scale": 0.125,
+                    "vdim": 128, "diff": 0.5, "scale": 0.125,
                     "mask": {"size": window, "keep_first": keep}, "rot": {"base": 10000.0, "dims": 32}}
     parallel = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
                          "scale": dim ** -0.5, "mask": {"size": window},

@@ -95,9 +95,9 @@ RAW = {
               moe(1, 1, 24)),
         layer("attention_2", differential(1, 1, 32, 32, 30, 30, 32, 0.0), dense(24, 100.0)),
     ], bigram=None),
-    "only_capped": model(48, 50, [layer("attention", capped(6, 2, 12, 17, 8, 5.0, scaling=(8.0, 1.0, 4.0, 64)),
+    "only_capped": model(48, 50, [layer("attention", capped(6, 2, 12, 17, 8, 5.0, scaling=(6.0, 1.0, 3.0, 64)),
                                         dense(64, 1.5))]),
-    "only_differential": model(48, 50, [layer("attention_2", differential(6, 2, 12, 20, 17, 7, 6, 0.6),
+    "only_differential": model(48, 50, [layer("attention_2", differential(6, 2, 12, 20, 17, 7, 6, 0.45),
                                               moe(4, 2, 16, shared=24))]),
     "only_parallel": model(48, 50, [layer("parallel", {"left": chunked(6, 2, 12, 20, 17, 8),
                                                        "right": retained(4, 12, 6, (0.9, 0.95, 0.99, 0.999), 12)},
@@ -126,8 +126,8 @@ RAW = {
     ], bigram=(211, 13, 1)),
     # layer sizes of the order a real model has (few layers, a small vocabulary)
     "real": model(512, 1000, [
-        layer("attention", capped(8, 2, 64, 128, 64, 50.0, scaling=(8.0, 1.0, 4.0, 256)), dense(1408, 7.0)),
-        layer("attention_2", differential(4, 2, 64, 128, 96, 16, 32, 0.6), moe(8, 2, 352, shared=704)),
+        layer("attention", capped(8, 2, 64, 128, 64, 30.0, scaling=(4.0, 1.0, 8.0, 256)), dense(1408, 7.0)),
+        layer("attention_2", differential(4, 2, 64, 128, 80, 16, 32, 0.55), moe(8, 2, 352, shared=704)),
         layer("parallel", {"left": chunked(8, 4, 64, 64, 128, 64), "right": retained(4, 64, 128, (0.97, 0.99, 0.995, 0.999), 64)},
               dense(1408, 7.0)),
     ], bigram=(4093, 1021, 17)),

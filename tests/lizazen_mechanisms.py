@@ -141,7 +141,7 @@ def check_scaled_rotation(ops, device, dtype):
     from mercury_b200.parts.rotary import RotaryEncoding
 
     stand = Stand(ops, device, dtype)
-    for dims, base, scaling in ((16, 10000.0, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}),
+    for dims, base, scaling in ((16, 10000.0, {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}),
                                 (6, 50.0, {"factor": 2.0, "low": 0.5, "high": 3.0, "original": 20}),
                                 (8, 300.0, None)):
         part = RotaryEncoding(dims + 4, base, dims, table_precision="float64", scaling=scaling)
@@ -193,6 +193,22 @@ def check_capped_window_attention(ops, device, dtype):
             assert (moved > 0.2) if query - key < window else (moved < 1e-9), (query, key, moved)
         run_attention(ops, device, dtype, spec, W, x, want, cuts_for(length, query, key), m["kv_heads"],
                       m["dim"], m["dim"], window, 0, f"capped attention q{query} k{key}")
+
+
+def check_far_key_among_hundreds(ops, device, dtype):
+    """A window of 200 keys over a prompt of 240: the one key that matters is 199 back (seen) or
+    200 back (not seen), among hundreds that weigh next to nothing, in a prompt and in decoding."""
+    m, W, spec = capped_case(window=200)
+    window, length = 200, 240
+    for query, key in ((235, 36), (235, 35), (239, 40), (216, 16)):
+        x = inputs_with_a_pair(length, query, key, 300 + query + key).to(dtype).float()
+        fn = lambda rows: plain.capped_window_attention(rows, m, double(W), "a.", 1e-6)
+        want = fn(x.double())
+        moved = weight_on(m, W, "a.", x, query, key, fn)
+        assert (moved > 0.2) if query - key < window else (moved < 1e-9), (query, key, moved)
+        cuts = [[length], [query - 3] + [1] * (length - query + 3), [100, 2, 77, length - 179]]
+        run_attention(ops, device, dtype, spec, W, x, want, cuts, m["kv_heads"], m["dim"], m["dim"],
+                      window, 0, f"far key q{query} k{key}")
 
 
 def differential_case(heads=4, kv_heads=2, dim=8, vdim=24, window=21, keep=5, rot=2, diff=0.35):
@@ -371,5 +387,6 @@ def check_experts_weighted_on_their_input(ops, device, dtype, experts=5, top=2, 
 
 
 ALL = [check_bigram_embedding, check_scaled_rotation, check_capped_window_attention,
+       check_far_key_among_hundreds,
        check_differential_attention, check_chunked_attention, check_retention,
        check_join_of_two_mixers, check_clamped_feed_forward, check_experts_weighted_on_their_input]
